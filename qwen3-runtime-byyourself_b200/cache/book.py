@@ -30,25 +30,29 @@ class CacheNeed:
     """What one layer's mixer asks of the cache.
 
     kind 'full': keys and values of every past token; 'window': of the last
-    `window` tokens; 'none': no keys.  `state_shape` is a fixed-size float32 area
-    per sequence (empty: none); it can go with any kind.
+    `window` tokens; 'chunk': of the tokens in the query's own chunk of `window`
+    positions (chunks counted from position 0); 'none': no keys.  `state_shape` is
+    a fixed-size float32 area per sequence (empty: none); it can go with any kind.
+    `value_dim` is the size of a value row where it differs from the key's `head_dim`.
     """
     kind: str = "none"
     num_kv_heads: int = 0
     head_dim: int = 0
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
+    value_dim: Optional[int] = None
 
     def __post_init__(self):
-        if self.kind not in ("full", "window", "none"):
+        if self.kind not in ("full", "window", "chunk", "none"):
             raise ValueError(f"unknown cache kind {self.kind!r}")
-        if self.kind == "window" and not (self.window and self.window > 0):
-            raise ValueError("a window group needs a positive window")
+        if self.kind in ("window", "chunk") and not (self.window and self.window > 0):
+            raise ValueError("a window or chunk group needs a positive size")
         if self.kind != "none" and (self.num_kv_heads <= 0 or self.head_dim <= 0):
             raise ValueError("a key/value group needs num_kv_heads and head_dim")
 
     def group_key(self):
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window if self.kind == "window" else None)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window if self.kind in ("window", "chunk") else None,
+                self.value_dim or self.head_dim)
 
 
 class CacheError(RuntimeError):
@@ -179,7 +183,7 @@ class CacheBook:
             group_layers[by_key[key]].append(layer)
             self.group_of_layer[layer] = by_key[key]
         G = len(group_needs)
-        kinds = (ctypes.c_int32 * max(G, 1))(*[1 if n.kind == "window" else 0 for n in group_needs])
+        kinds = (ctypes.c_int32 * max(G, 1))(*[{"window": 1, "chunk": 2}.get(n.kind, 0) for n in group_needs])
         windows = (ctypes.c_int32 * max(G, 1))(*[int(n.window or 0) for n in group_needs])
         handle = ctypes.c_void_p()
         code = _host().q3_book_create(kinds, windows, G, int(max_tokens), int(max_seq_len), int(n_slots or 0), PAGE_TOKENS,

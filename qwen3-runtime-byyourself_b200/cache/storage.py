@@ -1,6 +1,8 @@
 """The cache's device storage: pages of keys and values per group, state per layer.
 
-Layout of one group: [layer in group, K|V, page, kv head, token in page, head_dim].
+Layout of one group: [layer in group, K|V, page, kv head, token in page, head_dim];
+a group whose values have another size than its keys holds two such tensors, one for
+the keys and one, [..., value_dim], for the values.
 A (page, kv head) tile is one contiguous [PAGE_TOKENS, head_dim] panel, so a kernel
 streams whole panels and a 2-D bulk copy can fetch one.  State rows are float32
 [slot, *state_shape] per layer and are zeroed when the slot is handed out; row number
@@ -35,10 +37,15 @@ class KVCache(CacheBook):
                  dtype: torch.dtype, device, n_slots: Optional[int] = None, cache_from: Optional[Dict[int, int]] = None):
         super().__init__(needs, max_tokens, max_seq_len, n_slots)
         self.dtype, self.device = dtype, torch.device(device)
-        self.stores = [
-            torch.zeros((len(g.layers), 2, g.n_pages + 1, g.need.num_kv_heads, PAGE_TOKENS, g.need.head_dim),
-                        dtype=dtype, device=self.device)
-            for g in self.groups]
+        self.stores = []          # per group: one tensor [layer, K|V, ...], or a (keys, values) pair of [layer, ...]
+        for g in self.groups:
+            shape = (g.n_pages + 1, g.need.num_kv_heads, PAGE_TOKENS)
+            vd = g.need.value_dim or g.need.head_dim
+            if vd == g.need.head_dim:
+                self.stores.append(torch.zeros((len(g.layers), 2) + shape + (vd,), dtype=dtype, device=self.device))
+            else:
+                self.stores.append((torch.zeros((len(g.layers),) + shape + (g.need.head_dim,), dtype=dtype, device=self.device),
+                                    torch.zeros((len(g.layers),) + shape + (vd,), dtype=dtype, device=self.device)))
         self.states = {layer: torch.zeros((self.n_slots + 1,) + shape, dtype=torch.float32, device=self.device)
                        for layer, shape in self.state_layers.items()}
         self._views: Dict[int, LayerCache] = {}
@@ -49,7 +56,8 @@ class KVCache(CacheBook):
             keys = values = None
             if gi is not None:
                 li = self.groups[gi].layers.index(layer)
-                keys, values = self.stores[gi][li, 0], self.stores[gi][li, 1]
+                store = self.stores[gi]
+                keys, values = (store[0][li], store[1][li]) if isinstance(store, tuple) else (store[li, 0], store[li, 1])
             self._views[layer] = LayerCache(gi, keys, values, self.states.get(layer),
                                             need.window if need.kind == "window" else None)
         for layer, src in (cache_from or {}).items():
@@ -64,4 +72,5 @@ class KVCache(CacheBook):
 
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.layers) * 2 * g.need.num_kv_heads * g.need.head_dim * item for g in self.groups)
+        return sum(len(g.layers) * g.need.num_kv_heads * (g.need.head_dim + (g.need.value_dim or g.need.head_dim)) * item
+                   for g in self.groups)

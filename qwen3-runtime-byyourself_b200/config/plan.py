@@ -27,16 +27,32 @@ class LayerSpec:
     """
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]      # None: the layer has no feed-forward (its block must allow that)
     prefix: str
     cache_from: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StreamStep:
+    """A part that rewrites the hidden state between layers from the state and the embedding's output
+    (family `stream`): it runs right before entry `before_run` of the plan's `order`.  `name` is the
+    checkpoint name of its tensor (or the prefix of its tensors)."""
+    before_run: int
+    part: PartSpec
+    name: str
 
 
 @dataclass(frozen=True)
 class ModelPlan:
     """The whole model as data.
 
-    `order` is the sequence in which layers run; it may name a layer twice.
+    `order` is the sequence in which layers run; it may name a layer twice.  `caches` gives, for
+    every entry of `order`, the number of the cache (pages and state) that run uses: a layer that
+    runs several times with the same weights can keep one cache per run.  Numbers below the number
+    of layers are the layers' own caches, numbers from there on are further ones of the same kind
+    as the layer's that uses them.  None: every run of a layer uses the layer's own cache.
+    `stream_steps` run between layers; `residual_dtype` "float32" keeps the hidden state between
+    the parts in 32-bit whatever the compute type (None: in the compute type).
     """
     architecture: str
     vocab_size: int
@@ -51,9 +67,36 @@ class ModelPlan:
     head: PartSpec
     head_prefix: str
     stop_token_ids: List[int] = field(default_factory=list)
+    caches: Optional[List[int]] = None
+    stream_steps: List[StreamStep] = field(default_factory=list)
+    residual_dtype: Optional[str] = None
+    final_norm_name: Optional[str] = None     # the final norm's tensor (None: final_norm_prefix + "weight")
+
+    def cache_of_run(self, run: int) -> int:
+        return self.order[run] if self.caches is None else self.caches[run]
+
+    def cache_owners(self) -> List[Optional[int]]:
+        """For every cache number, the layer whose mixer states what the cache holds (None: unused)."""
+        owners: List[Optional[int]] = list(range(len(self.layers)))
+        for run, layer in enumerate(self.order):
+            unit = self.cache_of_run(run)
+            owners.extend([None] * (unit + 1 - len(owners)))
+            owners[unit] = layer
+        return owners
 
     def __post_init__(self):
         n = len(self.layers)
+        if self.caches is not None:
+            if len(self.caches) != len(self.order):
+                raise ValueError("caches names one cache for every entry of order")
+            for run, unit in enumerate(self.caches):
+                if unit < 0 or (unit < n and unit != self.order[run]):
+                    raise ValueError(f"run {run}: cache {unit} is another layer's own")
+        for step in self.stream_steps:
+            if not 0 <= step.before_run < len(self.order):
+                raise ValueError(f"a stream step before run {step.before_run}, but the plan has {len(self.order)} runs")
+        if self.residual_dtype not in (None, "float32"):
+            raise ValueError("residual_dtype is None (the compute type) or 'float32'")
         for i in self.order:
             if not 0 <= i < n:
                 raise ValueError(f"order names layer {i}, but the plan has {n} layers")

@@ -1,7 +1,8 @@
 """The one registry from an architecture's name to its configuration class.
 
-config.json names the architecture in `architectures`; the class registered
-under that name parses the rest of the file and produces the `ModelPlan`.
+config.json names the architecture in `architectures` (a list) or in `architecture`
+(one name); the class registered under that name parses the rest of the file and
+produces the `ModelPlan`.
 """
 from __future__ import annotations
 
@@ -40,9 +41,12 @@ def config_from_dict(root: dict, **options):
     (`options` go to its `from_dict`, e.g. `strict=True`)."""
     if not isinstance(root, dict):
         raise ConfigError("model config root must be a JSON object")
-    if "architectures" not in root:
+    if "architectures" not in root and isinstance(root.get("architecture"), str):
+        names = [root["architecture"]]
+    elif "architectures" not in root:
         raise ConfigError("missing required config field 'architectures'")
-    names = root["architectures"]
+    else:
+        names = root["architectures"]
     if not isinstance(names, list):
         raise ConfigError("config field 'architectures' must be an array")
     for name in names:

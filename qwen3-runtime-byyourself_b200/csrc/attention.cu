@@ -12,6 +12,12 @@
 //   attention   : causal grouped-query attention by loop bound, scale after the dot,
 //                 online softmax (src/ops/gqa_attention.cu:42-44,84-86,117,119-144,152).
 //
+// Beyond what Qwen3 needs, as parameters: a bias added to the projection output before the
+// rotation; values of another size than keys (`vd`); scores capped smoothly,
+// s <- cap * tanh(s / cap); a window of the last keys, or the keys of the query's own chunk
+// of positions (chunks of `chunk` positions counted from 0); and a sink, one more term
+// exp(0) in the softmax's denominator that carries no value.
+//
 // Cache layout: pages [page, kv head, PAGE tokens, head_dim]; `page_table[seq]` lists
 // the pages of a sequence in order.  Keys are visited page by page in ascending
 // position, so the result for one (position, head) does not depend on how the tokens
@@ -41,7 +47,8 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                    const float* __restrict__ k_norm_w, const float* __restrict__ cos_tab,
                                    const float* __restrict__ sin_tab, const int* __restrict__ token_seq,
                                    const int* __restrict__ token_pos, const int* __restrict__ page_table,
-                                   int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv, int rot) {
+                                   int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv, int rot,
+                                   const float* __restrict__ bias, int vd) {
     pdl_launch_dependents();
     pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -49,7 +56,11 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
     if (head >= nq + 2 * nkv || (head >= nq && !write_kv)) return;   // a layer that reads another layer's cache writes none
     const int64_t t = blockIdx.y;
     const int pos = token_pos[t];
-    const T* src = qkv + t * (int64_t)(nq + 2 * nkv) * d + (int64_t)head * d;
+    // a row of the projection: nq query heads and nkv key heads of d values, then nkv value heads of vd values
+    const int64_t row = (int64_t)(nq + nkv) * d + (int64_t)nkv * vd;
+    const int64_t col0 = head < nq + nkv ? (int64_t)head * d : (int64_t)(nq + nkv) * d + (int64_t)(head - nq - nkv) * vd;
+    const T* src = qkv + t * row + col0;
+    if (bias != nullptr) bias += col0;
 
     T* dst;
     const float* norm_w = nullptr;
@@ -61,9 +72,13 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
         const int kvh = (head - nq) % nkv;
         const bool is_v = head >= nq + nkv;
         const int page = page_table[(int64_t)token_seq[t] * pages_per_seq + pos / PAGE];
-        dst = (is_v ? v_pages : k_pages) + (((int64_t)page * nkv + kvh) * PAGE + pos % PAGE) * d;
+        dst = (is_v ? v_pages : k_pages) + (((int64_t)page * nkv + kvh) * PAGE + pos % PAGE) * (is_v ? vd : d);
         norm_w = is_v ? nullptr : k_norm_w;
         rotate = rotate && !is_v;
+        if (is_v) {                                     // a value head: vd values that pass through
+            d = vd;
+            rot = 0;
+        }
     }
 
     // The first `rot` values of the head are rotated in pairs (i, i + rot/2), i = lane + 32 n; the values from
@@ -78,6 +93,10 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
         if (i < rhalf) {
             a[n] = to_f32<T>(src[i]);
             b[n] = to_f32<T>(src[i + rhalf]);
+            if (bias != nullptr) {
+                a[n] = round_to<T>(a[n] + bias[i]);
+                b[n] = round_to<T>(b[n] + bias[i + rhalf]);
+            }
             sq += a[n] * a[n] + b[n] * b[n];
         }
     }
@@ -88,6 +107,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
             c[n] = 0.0f;
             if (i < d) {
                 c[n] = to_f32<T>(src[i]);
+                if (bias != nullptr) c[n] = round_to<T>(c[n] + bias[i]);
                 sq += c[n] * c[n];
             }
         }
@@ -213,7 +233,7 @@ __global__ void __launch_bounds__(128)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                          T* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                          const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, int d, float scale,
-                         int window) {
+                         int window, int vd, float softcap, int chunk, int sink) {
     __shared__ float q_s[MAX_HEAD_DIM];
     __shared__ float score[PAGE];
     __shared__ float prob[PAGE];
@@ -228,20 +248,23 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     for (int i = tid; i < d; i += 128) q_s[i] = to_f32<T>(q[(t * nq + head) * (int64_t)d + i]);
     __syncthreads();
 
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    float m_run = -INFINITY, l_run = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+    const int lo = window > 0 ? max(0, pos - window + 1) : (chunk > 0 ? pos / chunk * chunk : 0);
+    // the sink is a key of score 0 without a value: the running maximum and sum start from it
+    float m_run = sink ? 0.0f : -INFINITY, l_run = sink ? 1.0f : 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+    const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
     for (int pg = lo / PAGE; pg <= pos / PAGE; ++pg) {
-        const int64_t base = ((int64_t)pages[pg] * nkv + kvh) * PAGE * d;
-        const T* kp = k_pages + base;
-        const T* vp = v_pages + base;
+        const int64_t tile = ((int64_t)pages[pg] * nkv + kvh) * PAGE;
+        const T* kp = k_pages + tile * d;
+        const T* vp = v_pages + tile * vd;
         const int j_lo = max(lo - pg * PAGE, 0), j_hi = min(pos - pg * PAGE, PAGE - 1);  // inclusive, in-page
         for (int j = warp; j < PAGE; j += 4) {
             float dot = 0.0f;
             if (j >= j_lo && j <= j_hi) {
                 for (int i = lane; i < d; i += 32) dot = fmaf(q_s[i], to_f32<T>(kp[(int64_t)j * d + i]), dot);
             }
-            dot = warp_sum(dot);
-            if (lane == 0) score[j] = (j >= j_lo && j <= j_hi) ? dot * scale : -INFINITY;
+            dot = warp_sum(dot) * scale;
+            if (softcap > 0.0f) dot = softcap * tanhf(dot * inv_cap);
+            if (lane == 0) score[j] = (j >= j_lo && j <= j_hi) ? dot : -INFINITY;
         }
         __syncthreads();
         float m_new = m_run;
@@ -253,8 +276,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
         for (int j = j_lo; j <= j_hi; ++j) {
             const float p = prob[j];
             l_add += p;
-            if (tid < d) v0 = fmaf(p, to_f32<T>(vp[(int64_t)j * d + tid]), v0);
-            if (tid + 128 < d) v1 = fmaf(p, to_f32<T>(vp[(int64_t)j * d + tid + 128]), v1);
+            if (tid < vd) v0 = fmaf(p, to_f32<T>(vp[(int64_t)j * vd + tid]), v0);
+            if (tid + 128 < vd) v1 = fmaf(p, to_f32<T>(vp[(int64_t)j * vd + tid + 128]), v1);
         }
         l_run = l_run * alpha + l_add;
         acc0 = acc0 * alpha + v0;
@@ -262,22 +285,24 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
         m_run = m_new;
         __syncthreads();  // score/prob are rewritten by the next page
     }
-    T* o = out + (t * nq + head) * (int64_t)d;
-    if (tid < d) o[tid] = from_f32<T>(acc0 / l_run);
-    if (tid + 128 < d) o[tid + 128] = from_f32<T>(acc1 / l_run);
+    T* o = out + (t * nq + head) * (int64_t)vd;
+    if (tid < vd) o[tid] = from_f32<T>(acc0 / l_run);
+    if (tid + 128 < vd) o[tid + 128] = from_f32<T>(acc1 / l_run);
 }
 
 template <typename T>
 int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const float* q_norm_w, const float* k_norm_w,
                        const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos,
                        const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps,
-                       int write_kv, int rot, cudaStream_t stream) {
+                       int write_kv, int rot, const float* bias, int vd, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d <= 0 || d % 2 != 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0) return Q3_ERR_BAD_SIZE;
     if (rot <= 0) rot = d;                       // the whole head is rotated
     if (rot % 2 != 0 || rot > d) return Q3_ERR_BAD_SIZE;
+    if (vd <= 0) vd = d;                         // values as wide as keys
+    if (vd > MAX_HEAD_DIM) return Q3_ERR_BAD_SIZE;
     constexpr int VEC = Pack<T>::N;
-    if (rot == d && n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
+    if (rot == d && bias == nullptr && vd == d && n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
         aligned16(k_pages) && aligned16(v_pages)) {
         const int hpw = 32 / ((d / 2) / VEC);
         const int64_t n_warps = (n_tokens * (nq + 2 * nkv) + hpw - 1) / hpw;
@@ -291,19 +316,23 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
     const int warps = 4;
     const dim3 grid((nq + 2 * nkv + warps - 1) / warps, (unsigned)n_tokens);
     return (int)q3_launch(qkv_prepare_kernel<T>, grid, dim3(warps * 32), 0, stream, qkv, q_out, k_pages, v_pages, q_norm_w,
-                          k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps, write_kv, rot);
+                          k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps, write_kv, rot,
+                          bias, vd);
 }
 
 template <typename T>
 int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,
-                             int nkv, int d, float scale, int window, cudaStream_t stream) {
+                             int nkv, int d, float scale, int window, int vd, float softcap, int chunk, int sink,
+                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
+    if (vd <= 0) vd = d;
+    if (d <= 0 || d > MAX_HEAD_DIM || vd > MAX_HEAD_DIM || nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
+    if (window > 0 && chunk > 0) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const dim3 grid(nq, (unsigned)n_tokens);
     return (int)q3_launch(attention_generic_kernel<T>, grid, dim3(128), 0, stream, q, k_pages, v_pages, out, token_seq,
-                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window);
+                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window, vd, softcap, chunk, sink);
 }
 
 }  // namespace
@@ -313,18 +342,20 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
                                           const float* q_norm_w, const float* k_norm_w, const float* cos_tab,         \
                                           const float* sin_tab, const int* token_seq, const int* token_pos,           \
                                           const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,         \
-                                          int nkv, int d, float eps, int write_kv, int rotary_dim, void* stream) {   \
+                                          int nkv, int d, float eps, int write_kv, int rotary_dim,           \
+                                          const float* bias, int value_dim, void* stream) {                           \
         return qkv_prepare_launch<T>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, q_norm_w, k_norm_w, cos_tab, \
                                      sin_tab, token_seq, token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d,  \
-                                     eps, write_kv, rotary_dim, (cudaStream_t)stream);                                \
+                                     eps, write_kv, rotary_dim, bias, value_dim, (cudaStream_t)stream);               \
     }                                                                                                                 \
     Q3_EXPORT int q3_attention_generic_##SUFFIX(const void* q, const void* k_pages, const void* v_pages, void* out,   \
                                                 const int* token_seq, const int* token_pos, const int* page_table,    \
                                                 int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,          \
-                                                float scale, int window, void* stream) {                              \
+                                                float scale, int window, int value_dim, float softcap,     \
+                                                int chunk, int sink, void* stream) {                                  \
         return attention_generic_launch<T>((const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_seq,     \
                                            token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d, scale, window, \
-                                           (cudaStream_t)stream);                                                     \
+                                           value_dim, softcap, chunk, sink, (cudaStream_t)stream);                    \
     }
 
 Q3_ATTENTION_EXPORTS(f32, float)

@@ -203,9 +203,15 @@ static int rms_norm_launch(T* x, const T* delta, const float* w, T* y, int64_t r
 // gate_up: [rows, 2*inter]; out: [rows, inter].  Two layouts of a row: the gate in the first
 // `inter` columns and the up values in the rest, or (interleaved) blocks of eight gate
 // columns followed by the eight up columns of the same features.
+// act: 0 = SiLU, 1 = the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gate_activation(float z, int act) {
+    if (act == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
 template <typename T, int VEC>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int inter,
-                                int interleaved) {
+                                int interleaved, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int64_t per_row = inter / VEC;
@@ -219,15 +225,15 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
         load_vec<T, VEC>(gate_up + r * 2 * inter + gate_at, g);
         load_vec<T, VEC>(gate_up + r * 2 * inter + up_at, u);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) g[k] = round_to<T>(g[k] / (1.0f + expf(-g[k]))) * u[k];
+        for (int k = 0; k < VEC; ++k) g[k] = round_to<T>(gate_activation(g[k], act)) * u[k];
         store_vec<T, VEC>(out + r * inter + c, g);
     }
 }
 
 template <typename T>
-static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, int interleaved, cudaStream_t stream) {
+static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, int interleaved, int act, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (inter <= 0 || (interleaved && inter % 8 != 0)) return Q3_ERR_BAD_SIZE;
+    if (inter <= 0 || (interleaved && inter % 8 != 0) || act < 0 || act > 1) return Q3_ERR_BAD_SIZE;
     constexpr int V = Pack<T>::N;
     const bool vec = inter % V == 0 && aligned16(gate_up) && aligned16(out);
     const int threads = 256;
@@ -237,9 +243,9 @@ static int silu_mul_launch(const T* gate_up, T* out, int64_t rows, int inter, in
     if (blocks > resident) blocks = resident;
     if (vec)
         return (int)q3_launch(silu_mul_kernel<T, V>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows,
-                              inter, interleaved);
+                              inter, interleaved, act);
     return (int)q3_launch(silu_mul_kernel<T, 1>, dim3((unsigned)blocks), dim3(threads), 0, stream, gate_up, out, rows, inter,
-                          interleaved);
+                          interleaved, act);
 }
 
 // ---------------------------------------------------------------- gather rows (+ pending branch)
@@ -319,7 +325,11 @@ Q3_EXPORT int q3_place_rows(const void* src, int src_kind, void* dst, int dst_ki
     }                                                                                                               \
     Q3_EXPORT int q3_silu_mul_##SUFFIX(const void* gate_up, void* out, int64_t rows, int inter, int interleaved,    \
                                        void* stream) {                                                              \
-        return silu_mul_launch<T>((const T*)gate_up, (T*)out, rows, inter, interleaved, (cudaStream_t)stream);      \
+        return silu_mul_launch<T>((const T*)gate_up, (T*)out, rows, inter, interleaved, 0, (cudaStream_t)stream);   \
+    }                                                                                                               \
+    Q3_EXPORT int q3_act_mul_##SUFFIX(const void* gate_up, void* out, int64_t rows, int inter, int interleaved,     \
+                                      int act, void* stream) {                                                      \
+        return silu_mul_launch<T>((const T*)gate_up, (T*)out, rows, inter, interleaved, act, (cudaStream_t)stream); \
     }                                                                                                               \
     Q3_EXPORT int q3_gather_rows_##SUFFIX(const void* x, const void* delta, const int* idx, void* out, int64_t rows, \
                                           int size, void* stream) {                                                 \

@@ -42,13 +42,13 @@ qwen3::GenerationProgress* progress_of(void* h) { return static_cast<qwen3::Gene
 
 Q3_HOST_EXPORT const char* q3_host_last_error() { return g_error.c_str(); }
 
-// kinds[g]: 0 = every key, 1 = a window of windows[g] keys.
+// kinds[g]: 0 = every key, 1 = a window of windows[g] keys, 2 = the keys of the query's own chunk of windows[g] positions.
 Q3_HOST_EXPORT int q3_book_create(const int* kinds, const int* windows, int n_groups, int64_t max_tokens, int64_t max_seq_len,
                                   int n_slots, int page_tokens, void** out) {
     return guarded([&] {
         std::vector<qwen3::GroupNeed> needs(n_groups);
         for (int g = 0; g < n_groups; ++g) {
-            needs[g].kind = kinds[g] ? qwen3::GroupKind::Window : qwen3::GroupKind::Full;
+            needs[g].kind = kinds[g] == 2 ? qwen3::GroupKind::Chunk : kinds[g] ? qwen3::GroupKind::Window : qwen3::GroupKind::Full;
             needs[g].window = windows[g];
         }
         *out = new qwen3::CacheBook(needs, max_tokens, max_seq_len, n_slots, page_tokens);

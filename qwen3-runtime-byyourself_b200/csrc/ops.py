@@ -225,17 +225,20 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
-    """out[r, c] = silu(gate[r, c]) * up[r, c]; a row of `gate_up` holds the gate in its first half
-    and the up values in its second, or (`interleaved`) blocks of eight gate columns each followed
-    by the eight up columns of the same features."""
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False, activation: str = "silu") -> torch.Tensor:
+    """out[r, c] = act(gate[r, c]) * up[r, c], act = SiLU or (`activation="gelu_tanh"`) the tanh form of GELU; a row
+    of `gate_up` holds the gate in its first half and the up values in its second, or (`interleaved`) blocks of
+    eight gate columns each followed by the eight up columns of the same features."""
     s = _suffix(gate_up)
     rows, two_i = gate_up.shape
     if two_i % 2 or out.shape != (rows, two_i // 2) or out.dtype != gate_up.dtype:
         raise KernelError("silu_mul: output does not fit")
-    fn = _fn("elementwise.cu", f"q3_silu_mul_{s}", [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p])
-    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), rows, two_i // 2, int(bool(interleaved)), _stream()),
-           "silu_mul")
+    fn = _fn("elementwise.cu", f"q3_act_mul_{s}", [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), rows, two_i // 2, int(bool(interleaved)),
+              ACTIVATIONS[activation], _stream()), "silu_mul")
     return out
 
 
@@ -270,6 +273,72 @@ def place_rows(src: torch.Tensor, dst: torch.Tensor, block_rows: int = 0, dst_bl
     _check(fn(_dev(src, "src"), kinds[src.dtype], _dev(dst, "dst"), kinds[dst.dtype], rows, cols, block, stride, int(dst_row0),
               _stream()), "place_rows")
     return dst
+
+
+# ------------------------------------------------------------------ a hidden state kept in 32-bit (stream_f32.cu)
+def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale as float32, whatever the table's type."""
+    s = _suffix(table)
+    n = ids.numel()
+    if out.shape[0] < n or out.shape[1] != table.shape[1] or out.dtype != torch.float32:
+        raise KernelError("embedding_scaled: output does not fit")
+    fn = _fn("stream_f32.cu", f"q3_embedding_scaled_{s}", [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p])
+    _check(fn(_dev(ids, "ids", torch.int32), _dev(table, "table"), _dev(out, "out"), n, table.shape[1], table.shape[0],
+              float(scale), _stream()), "embedding_scaled")
+    return out
+
+
+def sandwich_norm(stream: torch.Tensor, branch: Optional[torch.Tensor], w_post: Optional[torch.Tensor], eps_post: float,
+                  w_pre: Optional[torch.Tensor], eps_pre: float, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """In one pass over the rows of the float32 `stream`: with `branch` (compute type), stream += RMSNorm(branch) *
+    w_post; with `out` (compute type), out = RMSNorm(stream) * w_pre of the sum.  Statistics and sums are 32-bit."""
+    rows, size = stream.shape
+    if stream.dtype != torch.float32 or (branch is None) != (w_post is None) or (out is None) != (w_pre is None):
+        raise KernelError("sandwich_norm: a float32 stream, a branch with its weights, an output with its weights")
+    ref = branch if branch is not None else out
+    if ref is None:
+        return None
+    for t in (branch, out):
+        if t is not None and (t.shape != stream.shape or t.dtype != ref.dtype):
+            raise KernelError("sandwich_norm: branch or output does not fit the stream")
+    for w in (w_post, w_pre):
+        if w is not None and w.numel() != size:
+            raise KernelError("sandwich_norm: weights do not fit the rows")
+    fn = _fn("stream_f32.cu", f"q3_sandwich_norm_{_suffix(ref)}",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_float, c_void_p])
+    _check(fn(_dev(stream, "stream"), _ptr(branch, "branch"), _ptr(w_post, "w_post", torch.float32),
+              _ptr(w_pre, "w_pre", torch.float32), _ptr(out, "out"), rows, size, float(eps_post), float(eps_pre), _stream()),
+           "sandwich_norm")
+    return out
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = [a[t]; b[t]] in out's type, from two float32 matrices of one shape."""
+    rows, size = a.shape
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != a.shape or out.shape != (rows, 2 * size):
+        raise KernelError("concat_cast: shapes do not fit")
+    fn = _fn("stream_f32.cu", f"q3_concat_cast_{_suffix(out)}", [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p])
+    _check(fn(_dev(a, "a"), _dev(b, "b"), _dev(out, "out"), rows, size, _stream()), "concat_cast")
+    return out
+
+
+def gather_rows_norm(stream: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = RMSNorm(stream[idx[r]]) * weight, from a float32 stream into out's type."""
+    rows, size = idx.numel(), stream.shape[-1]
+    if stream.dtype != torch.float32 or out.shape[0] < rows or out.shape[-1] != size or weight.numel() != size:
+        raise KernelError("gather_rows_norm: shapes do not fit")
+    fn = _fn("stream_f32.cu", f"q3_gather_rows_norm_{_suffix(out)}",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p])
+    _check(fn(_dev(stream, "stream"), _dev(idx, "idx", torch.int32), _dev(weight, "weight", torch.float32), _dev(out, "out"),
+              rows, size, float(eps), _stream()), "gather_rows_norm")
+    return out
+
+
+def scale_softcap(x: torch.Tensor, scale: float, cap: float = 0.0) -> torch.Tensor:
+    """In place on float32 `x`: x <- cap * tanh(x * scale / cap), or x * scale when `cap` is 0."""
+    fn = _fn("stream_f32.cu", "q3_scale_softcap_f32", [c_void_p, c_int64, c_float, c_float, c_void_p])
+    _check(fn(_dev(x, "x", torch.float32), x.numel(), float(scale), float(cap or 0.0), _stream()), "scale_softcap")
+    return x
 
 
 # ------------------------------------------------------------------ matrix products
@@ -311,38 +380,50 @@ def _rotary_dim(cos, sin, d: int) -> int:
 
 
 def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, token_seq, token_pos, page_table,
-                n_tokens: int, nq: int, nkv: int, d: int, eps: float, write_kv: bool = True):
+                n_tokens: int, nq: int, nkv: int, d: int, eps: float, write_kv: bool = True, bias=None,
+                value_dim: Optional[int] = None):
     """Per-head norm of q and k, rotation, and the write of k and v into the cache pages
-    (`write_kv=False`: only q is prepared, for a layer that reads another layer's cache)."""
+    (`write_kv=False`: only q is prepared, for a layer that reads another layer's cache).  `bias` (float32, one
+    value per column of the projection) is added first; `value_dim` is the size of a value head if not `d`."""
     s = _suffix(qkv)
-    if d % 16 != 0 or d > 256:
-        raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
-    if qkv.shape[-1] != (nq + 2 * nkv) * d or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d):
+    vd = int(value_dim or d)
+    if d % 2 != 0 or not 0 < d <= 256 or not 0 < vd <= 256:
+        raise KernelError(f"head_dim {d} / value_dim {vd} is not supported: even key sizes and any value size up to 256")
+    if qkv.shape[-1] != (nq + nkv) * d + nkv * vd or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) \
+            or v_pages.shape[1:] != (nkv, PAGE_TOKENS, vd) or (bias is not None and bias.numel() != qkv.shape[-1]):
         raise KernelError("qkv_prepare: shapes do not fit")
     rot = _rotary_dim(cos, sin, d)
     fn = _fn("attention.cu", f"q3_qkv_prepare_{s}",
-             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
+             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p])
     _check(fn(_dev(qkv, "qkv"), _dev(q_out, "q_out", qkv.dtype), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
               _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
               _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32),
               _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, d, float(eps),
-              int(bool(write_kv)), rot, _stream()), "qkv_prepare")
+              int(bool(write_kv)), rot, _ptr(bias, "bias", torch.float32), vd, _stream()), "qkv_prepare")
     return q_out
 
 
 def attention_generic(q, k_pages, v_pages, out, token_seq, token_pos, page_table, n_tokens: int, nq: int, nkv: int,
-                      d: int, scale: float, window: Optional[int] = None):
-    """Causal grouped-query attention of every token of the step over its sequence's pages."""
+                      d: int, scale: float, window: Optional[int] = None, value_dim: Optional[int] = None,
+                      softcap: float = 0.0, chunk: Optional[int] = None, sink: bool = False):
+    """Causal grouped-query attention of every token of the step over its sequence's pages.  `softcap` > 0 caps the
+    scores smoothly (s <- softcap * tanh(s / softcap)); `chunk`: a query reads only the keys of its own chunk of that
+    many positions; `sink`: one more term exp(0), without a value, in the softmax's denominator; `value_dim`: the
+    size of a value head (and of an output head) if not `d`."""
     s = _suffix(q)
-    if d % 16 != 0 or d > 256:
-        raise KernelError(f"head_dim {d} is not supported: multiples of 16 up to 256")
+    vd = int(value_dim or d)
+    if not 0 < d <= 256 or not 0 < vd <= 256:
+        raise KernelError(f"head_dim {d} / value_dim {vd} is not supported: sizes up to 256")
+    if window and chunk:
+        raise KernelError("attention: a window or chunks, not both")
     fn = _fn("attention.cu", f"q3_attention_generic_{s}",
-             [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_int, c_int, c_void_p])
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", q.dtype), _dev(v_pages, "v_pages", q.dtype),
               _dev(out, "out", q.dtype), _dev(token_seq, "token_seq", torch.int32),
               _dev(token_pos, "token_pos", torch.int32), _dev(page_table, "page_table", torch.int32),
-              page_table.shape[-1], n_tokens, nq, nkv, d, float(scale), int(window or 0), _stream()),
+              page_table.shape[-1], n_tokens, nq, nkv, d, float(scale), int(window or 0), vd, float(softcap or 0.0),
+              int(chunk or 0), int(bool(sink)), _stream()),
            "attention_generic")
     return out
 

@@ -6,7 +6,8 @@
 // values live in *pages* of `page_tokens` tokens; a slot holds, for every layer group, a list of
 // pages that covers its length.  Layers whose mixers ask the same of the cache form a *group* with
 // a page pool of its own; a group that needs only a window of keys returns the pages that fell out
-// of the window after each step.
+// of the window after each step, and a group whose queries read only the keys of their own chunk of
+// positions (chunks of a fixed size, counted from position 0) returns the pages of finished chunks.
 //
 // A step is three calls: reserve (all or nothing: a step that does not fit changes nothing), the
 // launch, then commit (lengths advance once) or cancel (the launch failed: the pages go back).
@@ -34,7 +35,7 @@ struct CacheFull : CacheError {
     using CacheError::CacheError;
 };
 
-enum class GroupKind : int { Full = 0, Window = 1 };
+enum class GroupKind : int { Full = 0, Window = 1, Chunk = 2 };
 
 // The pages of the layers that share one need.
 class PageGroup {
@@ -75,12 +76,18 @@ public:
                 r[i] = -1;
             }
     }
-    // Give back the pages that no later query of this sequence can read (window groups).
+    // Give back the pages that no later query of this sequence can read (window and chunk groups).
     void trim_window(int slot, int64_t length) {
-        if (kind_ != GroupKind::Window) return;
-        // a query at position >= length reads keys > length - window
-        int64_t dead = (length - window_ + 1) / page_tokens_;
-        if (length - window_ + 1 < 0) dead = 0;
+        if (kind_ == GroupKind::Full) return;
+        int64_t dead;
+        if (kind_ == GroupKind::Window) {
+            // a query at position >= length reads keys > length - window
+            dead = (length - window_ + 1) / page_tokens_;
+            if (length - window_ + 1 < 0) dead = 0;
+        } else {
+            // a query at position >= length reads keys from the start of its own chunk on
+            dead = (length / window_ * window_) / page_tokens_;
+        }
         int32_t* r = table_.data() + (size_t)slot * pages_per_slot_;
         for (int64_t i = first_live_[slot]; i < dead; ++i)
             if (r[i] >= 0) {
@@ -111,7 +118,7 @@ private:
 // What one layer group asks of the cache.
 struct GroupNeed {
     GroupKind kind = GroupKind::Full;
-    int window = 0;        // Window groups: the number of keys a query reads
+    int window = 0;        // Window groups: the number of keys a query reads; Chunk groups: the size of a chunk
 };
 
 class CacheBook {
@@ -129,7 +136,7 @@ public:
         held_.assign(n_slots_, 0);
         for (int s = n_slots_ - 1; s >= 0; --s) free_slots_.push_back(s);
         for (const GroupNeed& g : groups) {
-            if (g.kind == GroupKind::Window && g.window <= 0) throw std::invalid_argument("a window group needs a positive window");
+            if (g.kind != GroupKind::Full && g.window <= 0) throw std::invalid_argument("a window or chunk group needs a positive size");
             groups_.emplace_back(g.kind, g.window, n_pages_, n_slots_, pages_per_slot_, page_tokens);
         }
     }

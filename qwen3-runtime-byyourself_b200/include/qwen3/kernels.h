@@ -43,6 +43,9 @@ int q3_rms_norm_bf16(void* x, const void* delta, const float* w, void* y, int64_
 /* out = round(silu(gate)) * up; a row of gate_up holds the gate then the up values, or (interleaved) blocks of 8 + 8 */
 int q3_silu_mul_f32(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, void* stream);
 int q3_silu_mul_bf16(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, void* stream);
+/* the same with the activation as a parameter: act 0 = SiLU, 1 = the tanh form of GELU */
+int q3_act_mul_f32(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, int act, void* stream);
+int q3_act_mul_bf16(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, int act, void* stream);
 /* out[r] = x[idx[r]] (+ delta[idx[r]]) */
 int q3_gather_rows_f32(const void* x, const void* delta, const int* idx, void* out, int64_t rows, int size, void* stream);
 int q3_gather_rows_bf16(const void* x, const void* delta, const int* idx, void* out, int64_t rows, int size, void* stream);
@@ -51,22 +54,46 @@ int q3_gather_rows_bf16(const void* x, const void* delta, const int* idx, void* 
 int q3_place_rows(const void* src, int src_kind, void* dst, int dst_kind, int64_t rows, int64_t cols, int64_t block_rows,
                   int64_t dst_block_stride, int64_t dst_row0, void* stream);
 
+/* ---- stream_f32.cu: a hidden state kept in float32 between parts that compute in float32 or bfloat16 -------- */
+/* out[t] = table[ids[t]] * scale */
+int q3_embedding_scaled_f32(const int* ids, const void* table, float* out, int64_t n_tokens, int hidden, int vocab, float scale, void* stream);
+int q3_embedding_scaled_bf16(const int* ids, const void* table, float* out, int64_t n_tokens, int hidden, int vocab, float scale, void* stream);
+/* stream += RMSNorm(branch) * w_post (branch and w_post may both be null), then out = RMSNorm(stream) * w_pre (out and
+   w_pre may both be null), one pass over a row */
+int q3_sandwich_norm_f32(float* stream_rows, const void* branch, const float* w_post, const float* w_pre, void* out, int64_t rows,
+                         int size, float eps_post, float eps_pre, void* stream);
+int q3_sandwich_norm_bf16(float* stream_rows, const void* branch, const float* w_post, const float* w_pre, void* out, int64_t rows,
+                          int size, float eps_post, float eps_pre, void* stream);
+/* out[t] = [a[t]; b[t]] in the compute type */
+int q3_concat_cast_f32(const float* a, const float* b, void* out, int64_t rows, int size, void* stream);
+int q3_concat_cast_bf16(const float* a, const float* b, void* out, int64_t rows, int size, void* stream);
+/* out[r] = RMSNorm(stream_rows[idx[r]]) * w */
+int q3_gather_rows_norm_f32(const float* stream_rows, const int* idx, const float* w, void* out, int64_t rows, int size, float eps, void* stream);
+int q3_gather_rows_norm_bf16(const float* stream_rows, const int* idx, const float* w, void* out, int64_t rows, int size, float eps, void* stream);
+/* x <- cap * tanh(x * scale / cap) in place, x * scale for cap = 0 */
+int q3_scale_softcap_f32(float* x, int64_t n, float scale, float cap, void* stream);
+
 /* ---- attention.cu: every head size in steps of 16 up to 256, float32 and bfloat16 ------------------------ */
 /* per-head RMSNorm of q and k (weights may be null), rotation of the first rotary_dim values of a head (0: all of
-   them; tables [positions, rotary_dim/2], may be null), and the write of k and v into their pages (write_kv = 0: q only) */
+   them; tables [positions, rotary_dim/2], may be null), and the write of k and v into their pages (write_kv = 0: q only);
+   bias (may be null) is added to the row of the projection first; value_dim (0: d) is the size of a value head */
 int q3_qkv_prepare_f32(const void* qkv, void* q_out, void* k_pages, void* v_pages, const float* q_norm_w, const float* k_norm_w,
                        const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos, const int* page_table,
-                       int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim, void* stream);
+                       int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim,
+                       const float* bias, int value_dim, void* stream);
 int q3_qkv_prepare_bf16(const void* qkv, void* q_out, void* k_pages, void* v_pages, const float* q_norm_w, const float* k_norm_w,
                         const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos, const int* page_table,
-                        int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim, void* stream);
-/* causal grouped-query attention of every token over its sequence's pages; window 0 = every key */
+                        int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim,
+                       const float* bias, int value_dim, void* stream);
+/* causal grouped-query attention of every token over its sequence's pages; window 0 = every key; value_dim 0 = d;
+   softcap > 0: scores s <- softcap * tanh(s / softcap); chunk > 0: a query reads the keys of its own chunk of that many
+   positions only; sink != 0: one more term exp(0) in the softmax's denominator */
 int q3_attention_generic_f32(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
-                             float scale, int window, void* stream);
+                             float scale, int window, int value_dim, float softcap, int chunk, int sink, void* stream);
 int q3_attention_generic_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                               const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
-                              float scale, int window, void* stream);
+                              float scale, int window, int value_dim, float softcap, int chunk, int sink, void* stream);
 
 /* ---- attention_decode.cu (-DQ3_HEAD_DIM): one new token per sequence, bfloat16 ---------------------------- */
 int q3_attention_decode_head_dim(void);

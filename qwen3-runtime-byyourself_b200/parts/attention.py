@@ -7,6 +7,14 @@ output projection.  The three projections run as one product over the row-wise
 concatenation [Wq; Wk; Wv] made at bind time; norm, rotation and the cache write are
 one kernel.  Head counts, head size, scale, window, norm and position encoding are
 parameters; the part does not know its model.
+
+Further parameters, none of which Qwen3 uses: biases on the q/k/v projections, values of
+another size than keys (`value_dim`), scores capped smoothly (`softcap`: s <- c tanh(s / c)),
+chunked attention (`chunk`: a query reads the keys of its own chunk of that many positions,
+chunks counted from position 0 of the sequence), a sink (`sink`: the softmax's denominator has
+one more term exp(0), which carries no value), an interleaved rotary encoding (the rows of the
+q and k projections are reordered at load time so that the kernels' half-split rotation
+applies), and the checkpoint names of the tensors (`names`).
 """
 from __future__ import annotations
 
@@ -33,50 +41,91 @@ FUSED_DECODE_KERNELS = []
 FUSED_PROJECTION_KERNELS = []
 
 
+TENSOR_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+                "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+
+
 class GQAAttention(Part):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  qk_norm: Optional[PartSpec] = None, position: Optional[PartSpec] = None,
-                 window: Optional[int] = None, prefix: str = ""):
+                 window: Optional[int] = None, prefix: str = "", value_dim: Optional[int] = None, bias: bool = False,
+                 softcap: Optional[float] = None, chunk: Optional[int] = None, sink: bool = False,
+                 names: Optional[dict] = None):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        value_dim = int(value_dim or head_dim)
+        if head_dim % 2 or not 0 < head_dim <= 256 or not 0 < value_dim <= 256:
+            raise ValueError(f"head_dim {head_dim} (values {value_dim}): the attention kernels take even key sizes and any "
+                             f"value size up to 256 (the tensor-core kernels: multiples of 16)")
+        if window and chunk:
+            raise ValueError("attention takes a window or chunks, not both")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.scale, self.window, self.prefix = float(scale), window, prefix
+        self.value_dim, self.has_bias, self.sink = value_dim, bool(bias), bool(sink)
+        self.softcap = float(softcap) if softcap else 0.0
+        self.chunk = int(chunk) if chunk else None
+        self.names = dict(TENSOR_NAMES, **(names or {}))
         self.q_norm = build_part("norm", qk_norm) if qk_norm else None
         self.k_norm = build_part("norm", qk_norm) if qk_norm else None
         self.position = build_part("position", position) if position else None
-        self.w_qkv = self.w_o = None
+        self.w_qkv = self.w_o = self.bias = None
+        self.reordered = False       # the rows of the q and k projections follow the position encoding's kernel order
+        # what the kernels written for Qwen3's attention take
+        self.plain = not (self.has_bias or self.softcap or self.chunk or self.sink or value_dim != head_dim or head_dim % 16)
 
     # -- weights
     def weight_specs(self, prefix: str) -> dict:
-        p = prefix + self.prefix
-        nq, nkv, d, H = self.num_heads, self.num_kv_heads, self.head_dim, self.hidden_size
-        specs = {p + "q_proj.weight": WeightSpec((nq * d, H)), p + "k_proj.weight": WeightSpec((nkv * d, H)),
-                 p + "v_proj.weight": WeightSpec((nkv * d, H)), p + "o_proj.weight": WeightSpec((H, nq * d))}
+        p, n = prefix + self.prefix, self.names
+        nq, nkv, d, vd, H = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.hidden_size
+        specs = {p + n["q"]: WeightSpec((nq * d, H)), p + n["k"]: WeightSpec((nkv * d, H)),
+                 p + n["v"]: WeightSpec((nkv * vd, H)), p + n["o"]: WeightSpec((H, nq * vd))}
+        if self.has_bias:
+            specs.update({p + n["q_bias"]: WeightSpec((nq * d,), "bias"), p + n["k_bias"]: WeightSpec((nkv * d,), "bias"),
+                          p + n["v_bias"]: WeightSpec((nkv * vd,), "bias")})
         if self.q_norm is not None:
-            specs.update(self.q_norm.weight_specs(p + "q_norm.weight"))
-            specs.update(self.k_norm.weight_specs(p + "k_norm.weight"))
+            specs.update(self.q_norm.weight_specs(p + n["q_norm"]))
+            specs.update(self.k_norm.weight_specs(p + n["k_norm"]))
         return specs
 
     def bind(self, weights: dict, prefix: str, dtype, device) -> None:
-        p = prefix + self.prefix
-        self.w_qkv = fuse_rows(weights, [p + "q_proj.weight", p + "k_proj.weight", p + "v_proj.weight"])
-        self.w_o = weights.pop(p + "o_proj.weight").contiguous()
+        p, n = prefix + self.prefix, self.names
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        self.w_qkv = fuse_rows(weights, [p + n["q"], p + n["k"], p + n["v"]])
+        self.w_o = weights.pop(p + n["o"]).contiguous()
+        if self.has_bias:
+            tensors = [weights[p + n[k]] for k in ("q_bias", "k_bias", "v_bias")]
+            getattr(weights, "wait", lambda: None)()          # a streamed checkpoint: the tensors are in place now
+            self.bias = torch.cat([t.to(device=device, dtype=torch.float32).reshape(-1) for t in tensors]).contiguous()
+        order = self.position.kernel_order() if self.position is not None and hasattr(self.position, "kernel_order") else None
+        if order is not None:
+            # q.k does not change when the values of every query and key head are reordered alike: put the pairs
+            # of the rotation where the kernels expect them, once
+            if self.q_norm is not None:
+                raise ValueError("an interleaved rotation with per-head norm weights is not supported")
+            getattr(weights, "wait", lambda: None)()
+            rows = (torch.arange(nq + nkv, device=self.w_qkv.device)[:, None] * d
+                    + torch.tensor(order, device=self.w_qkv.device)[None, :]).reshape(-1)
+            self.w_qkv[:rows.numel()] = self.w_qkv[:rows.numel()][rows]
+            if self.bias is not None:
+                self.bias[:rows.numel()] = self.bias[:rows.numel()][rows]
+            self.reordered = True
         if self.q_norm is not None:
-            self.q_norm.bind(weights, p + "q_norm.weight", dtype, device)
-            self.k_norm.bind(weights, p + "k_norm.weight", dtype, device)
+            self.q_norm.bind(weights, p + n["q_norm"], dtype, device)
+            self.k_norm.bind(weights, p + n["k_norm"], dtype, device)
 
     # -- cache
     def cache_need(self) -> CacheNeed:
-        return CacheNeed("window" if self.window else "full", self.num_kv_heads, self.head_dim, self.window)
+        kind = "window" if self.window else ("chunk" if self.chunk else "full")
+        return CacheNeed(kind, self.num_kv_heads, self.head_dim, self.window or self.chunk,
+                         value_dim=self.value_dim if self.value_dim != self.head_dim else None)
 
     # -- step
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
-        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        nq, nkv, d, vd = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
         N = ctx.n_tokens
         table = ctx.page_tables[cache.group]
-        attn = ctx.scratch.get("attn.ctx", (N, nq * d), ctx.dtype)
+        attn = ctx.scratch.get("attn.ctx", (N, nq * vd), ctx.dtype)
         out = ctx.scratch.get("mixer.out", (N, self.hidden_size), ctx.dtype)
         norm_eps = self.q_norm.eps if self.q_norm is not None else 0.0
         qw = self.q_norm.weight if self.q_norm is not None else None
@@ -92,7 +141,7 @@ class GQAAttention(Part):
                 if kernel(self, x, cache, q, ctx, table, qw, kw, norm_eps, cos, sin):
                     self.attend(q, cache, attn, ctx, table)
                     return linear(attn, self.w_o, out)
-        qkv = ctx.scratch.get("attn.qkv", (N, (nq + 2 * nkv) * d), ctx.dtype)
+        qkv = ctx.scratch.get("attn.qkv", (N, (nq + nkv) * d + nkv * vd), ctx.dtype)
         linear(x, self.w_qkv, qkv)
         if tables and ctx.is_decode and ctx.dtype == torch.bfloat16:
             for kernel in FUSED_DECODE_KERNELS:
@@ -101,7 +150,7 @@ class GQAAttention(Part):
         q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
         if tables:
             ops.qkv_prepare(qkv, q, cache.keys, cache.values, qw, kw, cos, sin, ctx.token_seq, ctx.token_pos, table,
-                            N, nq, nkv, d, norm_eps, write_kv=not cache.shared)
+                            N, nq, nkv, d, norm_eps, write_kv=not cache.shared, bias=self.bias, value_dim=vd)
         else:
             self._prepare_unfused(qkv, q, cache, ctx, table, qw, kw, norm_eps)
         self.attend(q, cache, attn, ctx, table)
@@ -113,12 +162,15 @@ class GQAAttention(Part):
                 if kernel(self, q, cache, out, ctx, table):
                     return
         ops.attention_generic(q, cache.keys, cache.values, out, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
-                              self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window)
+                              self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
+                              value_dim=self.value_dim, softcap=self.softcap, chunk=self.chunk, sink=self.sink)
 
     def _prepare_unfused(self, qkv, q, cache, ctx, table, qw, kw, eps) -> None:
         """A position encoding without kernel tables: norm, then `apply_`, then the cache write."""
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         N = ctx.n_tokens
+        if self.bias is not None:
+            qkv = (qkv.float() + self.bias).to(qkv.dtype)
         qs = qkv[:, :nq * d].contiguous().view(N, nq, d)
         ks = qkv[:, nq * d:(nq + nkv) * d].contiguous().view(N, nkv, d)
         if qw is not None:                                  # into buffers of their own: the norm kernel's input and
@@ -127,14 +179,19 @@ class GQAAttention(Part):
             ops.rms_norm(ks, kw, eps, kn)
             qs, ks = qn, kn
         self.position.prepare(ctx.max_positions, ctx.device)
-        self.position.apply_(qs, ks, ctx.token_pos[:N])
+        if self.reordered:
+            self.position.apply_(qs, ks, ctx.token_pos[:N], kernel_order=True)
+        else:
+            self.position.apply_(qs, ks, ctx.token_pos[:N])
         packed = torch.cat([qs.view(N, -1), ks.view(N, -1), qkv[:, (nq + nkv) * d:]], dim=1).contiguous()
         ops.qkv_prepare(packed, q, cache.keys, cache.values, None, None, None, None, ctx.token_seq, ctx.token_pos,
-                        table, N, nq, nkv, d, 0.0, write_kv=not cache.shared)
+                        table, N, nq, nkv, d, 0.0, write_kv=not cache.shared, value_dim=self.value_dim)
 
 
 def _decode_split_kernel(part, q, cache, out, ctx, table) -> bool:
     """The split-key tensor-core decode kernel: bfloat16, groups of up to 16 query heads."""
+    if not part.plain:
+        return False
     nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
     if nq // nkv > 16:
         return False
@@ -148,6 +205,8 @@ def _decode_split_kernel(part, q, cache, out, ctx, table) -> bool:
 def _decode_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
     """Norm, rotation, cache write, split-key attention and the merge of the splits (inside a thread-block
     cluster) in one launch: bfloat16, groups of up to 16 query heads, up to 16 splits."""
+    if not part.plain:
+        return False
     nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
     if nq // nkv > 16:
         return False
@@ -167,6 +226,8 @@ def _decode_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, 
 def _projection_pair_kernel(part, x, cache, q, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
     """The q/k/v product on pairs of SMs with norm, rotation and the cache write in its epilogue, where `linear`
     would take the persistent pairs kernel anyway: head sizes 64, 128 and 256, the whole head rotated."""
+    if not part.plain:
+        return False
     from . import linear as linear_module
     nq, nkv, d = part.num_heads, part.num_kv_heads, part.head_dim
     N, K = ctx.n_tokens, part.hidden_size
@@ -195,6 +256,8 @@ def _sm_count(device) -> int:
 
 def _prefill_flash_kernel(part, q, cache, out, ctx, table) -> bool:
     """The tiled tensor-core kernel for steps that bring prompts (or any mix of lengths)."""
+    if not part.plain:
+        return False
     ops.attention_prefill(q, cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table, ctx.n_seqs,
                           ctx.max_new, part.num_heads, part.num_kv_heads, part.head_dim, part.scale, part.window)
     return True
@@ -203,6 +266,8 @@ def _prefill_flash_kernel(part, q, cache, out, ctx, table) -> bool:
 def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
     """Both products of the attention on tcgen05 with TMA-fed tiles: head sizes 64 and 128, no window,
     and enough new tokens for 128-row tiles to be worth it."""
+    if not part.plain:
+        return False
     if not ops.attention_prefill_tc_fits(part.head_dim, part.window) or ctx.max_new < tc_prefill_rows or part.scale <= 0:
         return False
     ops.attention_prefill_tc(q[:ctx.n_tokens], cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table,

@@ -23,6 +23,8 @@ Interfaces (duck-typed; `Part` gives the defaults):
                   the hidden state is residual + delta, the sum is left to the next norm.
   embedding       forward(token_ids, out) -> [N, hidden]
   head            forward(x, out) -> float32 logits [R, vocab]
+  stream          a step between layers: weight_specs(name), bind(weights, name, dtype, device),
+                  forward(residual, delta, x0, ctx) -> (residual, delta), x0 being the embedding's output
 """
 from __future__ import annotations
 
@@ -37,14 +39,15 @@ FEED_FORWARDS: Dict[str, Callable] = {}
 BLOCKS: Dict[str, Callable] = {}
 EMBEDDINGS: Dict[str, Callable] = {}
 HEADS: Dict[str, Callable] = {}
+STREAMS: Dict[str, Callable] = {}
 
 _ALL = {"norm": NORMS, "position": POSITIONS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "block": BLOCKS,
-        "embedding": EMBEDDINGS, "head": HEADS}
+        "embedding": EMBEDDINGS, "head": HEADS, "stream": STREAMS}
 
 
 def register_part(family: str, kind: str, factory: Callable) -> None:
     """Make `factory(**params)` the builder of parts of `kind` in `family`
-    (norm, position, mixer, feed_forward, block, embedding, head)."""
+    (norm, position, mixer, feed_forward, block, embedding, head, stream)."""
     _ALL[family][kind] = factory
 
 

@@ -28,8 +28,13 @@ class Model:
         self.blocks = []
         for spec in plan.layers:
             mixer = build_part("mixer", spec.mixer)
-            feed_forward = build_part("feed_forward", spec.feed_forward)
+            feed_forward = build_part("feed_forward", spec.feed_forward) if spec.feed_forward is not None else None
             self.blocks.append(build_part("block", spec.block, mixer, feed_forward))
+        self.stream_steps = {}            # run -> (part, tensor name): what rewrites the hidden state before that run
+        for step in plan.stream_steps:
+            self.stream_steps[step.before_run] = (build_part("stream", step.part), step.name)
+        self.residual_dtype = torch.float32 if plan.residual_dtype == "float32" else None
+        self.final_norm_name = plan.final_norm_name or plan.final_norm_prefix + "weight"
         self.final_norm = build_part("norm", plan.final_norm)
         self.head = build_part("head", plan.head)
         self.dtype: Optional[torch.dtype] = None
@@ -42,7 +47,9 @@ class Model:
         specs = dict(self.embedding.weight_specs(p.embedding_prefix))
         for spec, block in zip(p.layers, self.blocks):
             specs.update(block.weight_specs(spec.prefix))
-        specs.update(self.final_norm.weight_specs(p.final_norm_prefix + "weight"))
+        for part, name in self.stream_steps.values():
+            specs.update(part.weight_specs(name))
+        specs.update(self.final_norm.weight_specs(self.final_norm_name))
         specs.update(self.head.weight_specs(p.head_prefix))
         return specs
 
@@ -62,7 +69,9 @@ class Model:
         p = self.plan
         self.dtype, self.device = dtype, torch.device(device)
         self.embedding.bind(weights, p.embedding_prefix, dtype, device)
-        self.final_norm.bind(weights, p.final_norm_prefix + "weight", dtype, device)
+        self.final_norm.bind(weights, self.final_norm_name, dtype, device)
+        for part, name in self.stream_steps.values():
+            part.bind(weights, name, dtype, device)
         self.head.bind(weights, p.head_prefix, dtype, device)
         for spec, block in zip(p.layers, self.blocks):
             block.bind(weights, spec.prefix, dtype, device)
@@ -75,8 +84,15 @@ class Model:
 
     # -- cache
     def cache_needs(self) -> List[Optional[CacheNeed]]:
-        return [None if spec.cache_from is not None else block.mixer.cache_need()
-                for spec, block in zip(self.plan.layers, self.blocks)]
+        """What every cache of the plan holds, by cache number: a layer's own, and the further ones of layers
+        that keep one cache per run."""
+        needs = []
+        for owner in self.plan.cache_owners():
+            if owner is None or self.plan.layers[owner].cache_from is not None:
+                needs.append(None)
+            else:
+                needs.append(self.blocks[owner].mixer.cache_need())
+        return needs
 
     def cache_sources(self) -> Dict[int, int]:
         return {i: spec.cache_from for i, spec in enumerate(self.plan.layers) if spec.cache_from is not None}
@@ -86,16 +102,33 @@ class Model:
         """Runs the step's tokens through every layer (filling the cache); returns float32
         logits [n_want, vocab] for the wanted rows, or None if none is wanted."""
         N, H = ctx.n_tokens, self.plan.hidden_size
-        residual = ctx.scratch.get("model.residual", (N, H), ctx.dtype)
+        stream_dtype = self.residual_dtype or ctx.dtype
+        residual = ctx.scratch.get("model.residual", (N, H), stream_dtype)
         self.embedding.forward(ctx.token_ids[:N], residual)
+        x0 = None
+        if self.stream_steps:                              # the embedding's output is read again later: keep it
+            x0 = residual
+            if 0 not in self.stream_steps:                 # the first layers work on a copy
+                residual = ctx.scratch.get("model.residual_copy", (N, H), stream_dtype)
+                residual.copy_(x0)
         delta = None
-        for index in self.plan.order:
-            residual, delta = self.blocks[index].forward(residual, delta, ctx, cache.layer(index))
+        for run, index in enumerate(self.plan.order):
+            step = self.stream_steps.get(run)
+            if step is not None:
+                residual, delta = step[0].forward(residual, delta, x0, ctx)
+            residual, delta = self.blocks[index].forward(residual, delta, ctx, cache.layer(self.plan.cache_of_run(run)))
         if ctx.n_want == 0:
             return None
         R = ctx.n_want
         normed = ctx.scratch.get("model.rows_normed", (R, H), ctx.dtype)
-        if ctx.want_all:                                   # a decode step: the last residual sum rides in the norm
+        if self.residual_dtype is not None:                # a float32 stream: its pending sum and norms have kernels of their own
+            from .block import settle
+            if ctx.want_all:
+                settle(residual, delta, self.final_norm, normed)
+            else:
+                settle(residual, delta)
+                ops.gather_rows_norm(residual, ctx.want_rows[:R], self.final_norm.weight, self.final_norm.eps, normed)
+        elif ctx.want_all:                                 # a decode step: the last residual sum rides in the norm
             self.final_norm(residual, normed, delta)
         else:
             rows = ctx.scratch.get("model.rows", (R, H), ctx.dtype)

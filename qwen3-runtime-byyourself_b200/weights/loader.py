@@ -35,7 +35,8 @@ NORM_STD = 0.1
 @dataclass(frozen=True)
 class WeightSpec:
     """Shape and role of one checkpoint tensor.  Roles: 'matrix' (a projection or
-    an embedding table), 'norm' (a scale vector around 1), 'int_table' (int32)."""
+    an embedding table), 'norm' (a scale vector around 1), 'bias' (a vector around 0 that is
+    used in 32-bit), 'int_table' (int32)."""
     shape: Tuple[int, ...]
     role: str = "matrix"
 

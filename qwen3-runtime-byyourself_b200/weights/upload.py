@@ -32,7 +32,7 @@ ALIGN = 256
 
 
 def _role_dtype(role: str, compute: torch.dtype) -> torch.dtype:
-    return {"matrix": compute, "norm": torch.float32, "int_table": torch.int32}[role]
+    return {"matrix": compute, "norm": torch.float32, "bias": torch.float32, "int_table": torch.int32}[role]
 
 
 def fuse_rows(weights, names: Sequence[str]) -> torch.Tensor:
@@ -140,6 +140,11 @@ class CheckpointUpload:
         self._place(first, out, block, 2 * block, 0)
         self._place(second, out, block, 2 * block, block)
         return out
+
+    def wait(self) -> None:
+        """Work on the current stream that follows sees every tensor handed out so far in place (a part that
+        rearranges its tensors at bind time calls this first)."""
+        torch.cuda.current_stream(self.device).wait_stream(self._side)
 
     def finish(self) -> None:
         """Wait for the copies and kernels in flight and give the staging buffers back."""
