@@ -95,6 +95,19 @@ int q3_attention_generic_bf16(const void* q, const void* k_pages, const void* v_
                               const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
                               float scale, int window, int value_dim, float softcap, int chunk, int sink, void* stream);
 
+/* ---- attention_capped.cu (-DQ3_HEAD_DIM, -DQ3_VALUE_DIM): bfloat16 attention with scores capped by softcap * tanh(s / softcap)
+   (0: none), chunked visibility (chunk 0: causal only), a sink term in the softmax's denominator, values of their own size */
+int q3_attention_capped_head_dim(void);
+int q3_attention_capped_value_dim(void);
+int q3_attention_capped_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_start,
+                                     const int* seq_pos0, const int* page_table, int pages_per_seq, int n_seqs, int max_new, int nq,
+                                     int nkv, float scale, float softcap, int chunk, int sink, void* stream);
+/* one new token per sequence; scratch: n_tokens * nq * n_splits * (value_dim + 2) float32 */
+int q3_attention_capped_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
+                                    const int* token_seq, const int* token_pos, const int* page_table, int pages_per_seq,
+                                    int64_t n_tokens, int nq, int nkv, float scale, float softcap, int chunk, int sink, int n_splits,
+                                    void* stream);
+
 /* ---- attention_decode.cu (-DQ3_HEAD_DIM): one new token per sequence, bfloat16 ---------------------------- */
 int q3_attention_decode_head_dim(void);
 int64_t q3_attention_decode_scratch_floats(int64_t n_tokens, int nq, int n_splits);

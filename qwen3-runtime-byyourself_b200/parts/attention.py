@@ -276,6 +276,28 @@ def _prefill_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
     return True
 
 
+def _prefill_capped_kernel(part, q, cache, out, ctx, table) -> bool:
+    """Capped scores, chunks, a sink, values of their own size: the tiled tensor-core kernel for those."""
+    if part.plain or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, 1):
+        return False
+    ops.attention_capped_prefill(q, cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table, ctx.n_seqs, ctx.max_new,
+                                 part.num_heads, part.num_kv_heads, part.head_dim, part.value_dim, part.scale, part.softcap,
+                                 part.chunk, part.sink)
+    return True
+
+
+def _decode_capped_kernel(part, q, cache, out, ctx, table) -> bool:
+    """The same for decode steps: split over the keys of the chunk (or of the whole context), merged with the sink."""
+    nq, nkv = part.num_heads, part.num_kv_heads
+    if part.plain or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
+        return False
+    splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device), part.chunk or ctx.max_context)
+    scratch = ctx.scratch.get("attn.capped_scratch", (ctx.n_tokens * nq * splits * (part.value_dim + 2),), torch.float32)
+    ops.attention_capped_decode(q, cache.keys, cache.values, out, scratch, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
+                                nq, nkv, part.head_dim, part.value_dim, part.scale, part.softcap, part.chunk, part.sink, splits)
+    return True
+
+
 long_context_keys = 4096  # a decode step whose sequences may be longer takes wider clusters (if they are few)
 wide_cluster_blocks = 200 # blocks of a decode step with clusters beyond the portable size
 tc_prefill_rows = 128     # from this many new tokens of the longest sequence on, the tcgen05 kernel runs
@@ -289,5 +311,7 @@ FUSED_DECODE_KERNELS.append(_decode_fused_kernel)
 FUSED_PROJECTION_KERNELS.append(_projection_pair_kernel)
 PREFILL_KERNELS.append(_prefill_tcgen05_kernel)
 PREFILL_KERNELS.append(_prefill_flash_kernel)
+PREFILL_KERNELS.append(_prefill_capped_kernel)
+DECODE_KERNELS.append(_decode_capped_kernel)
 
 register_part("mixer", "gqa_attention", GQAAttention)
