@@ -260,6 +260,7 @@ def test_tensor_core_attention_over_pages_at_every_edge(nq, nkv, d, vd, scale, c
             assert np.allclose(got[i], want[i], atol=tol, rtol=tol), (label, key, float(np.abs(got[i] - want[i]).max()))
 
     def prompt(starts):
+        starts = [min(a, n - 1) for a, n in zip(starts, lengths)]
         tokens = [(s, p) for s, n in enumerate(lengths) for p in range(starts[s], n)]
         q = paged.queries(tokens, nq, "bfloat16", seed=sum(starts) + 1)
         counts = [n - a for n, a in zip(lengths, starts)]
