@@ -2,6 +2,7 @@
 model with random weights in bfloat16 on one B200, batch 8 at a context of 4,096 tokens.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 8b|14b|32b]
+    python bench.py --designs        (another measurement: a Dozazen model beside Qwen3 at equal sizes)
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.
   value     decoded tokens a second, timed on the device with CUDA events around K steps;
@@ -337,6 +338,92 @@ def kernel_breakdown(q, engine, sampler, torch, rng, batch, context, cfg, layers
     return out
 
 
+# Sizes for `--designs`: (name, width, query heads, kv heads, head size, feed-forward width, layers)
+DESIGN_SIZES = [("2k", 2048, 16, 4, 128, 8192, 4), ("4k", 4096, 32, 8, 128, 12288, 4)]
+DESIGN_VOCAB = 32768
+
+
+def design_configs(width, heads, kv, d, ff, layers, chunk):
+    """A Dozazen model and the Qwen3 model of the same widths, heads and layer count."""
+    mixer = {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 30.0, "mask": {"size": chunk},
+             "rot": {"base": 1000000.0, "dims": d, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    dozazen = {"architecture": "Dozazen", "vocab": DESIGN_VOCAB, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+               "logit_scale": 1.0, "logit_softcap": 30.0, "loop": {"start": 0, "stop": layers, "times": 1},
+               "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}} for _ in range(layers)]}
+    qwen3 = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
+                 head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB)
+    return dozazen, qwen3
+
+
+def design_point(q, torch, Sampler, cfg, rng, batch, context, steps, warmup):
+    """Decode and prompt throughput of one model, and the microseconds per entry point of one step of each kind."""
+    from qwen3_b200.csrc import ops
+    engine = q.Engine.from_random(q.config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=batch * context, max_seq_len=context)
+    sampler = Sampler(q.SamplingParams(mode="greedy"), engine.vocab_size, engine.device)
+    head = decode_run(q, engine, sampler, torch, rng, batch, context - warmup - steps - 1, steps, warmup)
+    times = []
+    for rep in range(5):
+        slot = engine.new_sequence()
+        prompt = rng.integers(0, engine.vocab_size, size=PREFILL_TOKENS).tolist()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([q.StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.release(slot)
+        if rep >= 2:
+            times.append(start.elapsed_time(stop))
+    out = {"decode_tok_s": round(head["tok_s"], 1), "decode_ms": round(head["ms"], 4),
+           "prefill_tok_s": round(PREFILL_TOKENS / statistics.median(times) * 1e3, 1), "prefill_ms": round(statistics.median(times), 3)}
+    # every kernel by itself: a decode step at the context, a prompt step
+    engine.use_graphs = False
+    lengths = unequal_lengths(batch, context - 8, rng)
+    slots = [engine.new_sequence() for _ in range(batch)]
+    piece = max(1, 8192 // max(lengths))
+    for lo in range(0, batch, piece):
+        part = range(lo, min(batch, lo + piece))
+        engine.step([q.StepEntry(slots[i], rng.integers(0, engine.vocab_size, size=lengths[i]).tolist(), []) for i in part])
+    entries = [q.StepEntry(s, [1], [0]) for s in slots]
+    for _ in range(2):
+        engine.step(entries)
+    with ops.KernelTimer() as timer:
+        engine.step(entries)
+    out["decode_step_us"] = {k: [n, round(us, 1)] for k, (n, us) in sorted(timer.summary().items())}
+    for s in slots:
+        engine.release(s)
+    prompt = rng.integers(0, engine.vocab_size, size=PREFILL_TOKENS).tolist()
+    for rep in range(3):
+        slot = engine.new_sequence()
+        if rep < 2:
+            engine.step([q.StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        else:
+            with ops.KernelTimer() as timer:
+                engine.step([q.StepEntry(slot, prompt, [PREFILL_TOKENS - 1])])
+        engine.release(slot)
+    out["prompt_step_us"] = {k: [n, round(us, 1)] for k, (n, us) in sorted(timer.summary().items())}
+    engine.check_kernels()
+    del engine, sampler
+    torch.cuda.empty_cache()
+    return out
+
+
+def designs_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096):
+    """Dozazen beside Qwen3 at equal sizes (random weights, bfloat16): decode at `batch` x `context`, a prompt step of
+    2,048 tokens; chunks longer than the context (every key is read, as in Qwen3) and chunks of 1,024."""
+    import numpy as np
+    out = {"batch": batch, "context": context, "prompt_tokens": PREFILL_TOKENS, "vocab": DESIGN_VOCAB, "sizes": {}}
+    for name, width, heads, kv, d, ff, layers in DESIGN_SIZES:
+        row = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": d, "ff": ff, "layers": layers}
+        for label, chunk in (("dozazen_chunk_8192", 8192), ("dozazen_chunk_1024", 1024)):
+            row[label] = design_point(q, torch, Sampler, design_configs(width, heads, kv, d, ff, layers, chunk)[0],
+                                      np.random.default_rng(0), batch, context, steps, warmup)
+        row["qwen3"] = design_point(q, torch, Sampler, design_configs(width, heads, kv, d, ff, layers, 8192)[1],
+                                    np.random.default_rng(0), batch, context, steps, warmup)
+        out["sizes"][name] = row
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -356,6 +443,9 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the benchmark: time every kernel of one decode step and of one 2,048-token prompt step "
                          "with CUDA events (steps launched afresh, not replayed) and print the sums per entry point")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the benchmark: decode and prompt throughput of a Dozazen model beside the Qwen3 model of the "
+                         "same widths at two sizes, with the time of every kernel of one step of each kind")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -374,6 +464,10 @@ def main() -> int:
     from qwen3_b200.sampling.sampler import Sampler
 
     cfg, CONTEXT, shape_batch = SHAPES[args.shape]
+    if args.designs:
+        torch.cuda.set_device(0)
+        print(json.dumps(designs_side_by_side(q, torch, Sampler, min(args.steps, 64), warmup, args.batch or 8, args.context or 4096)))
+        return 0
     if args.products:
         torch.cuda.set_device(0)
         counts = tuple(args.tokens) if args.tokens else (129, 256, 512, 1024, 2048, 4096)

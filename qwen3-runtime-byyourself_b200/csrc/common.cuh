@@ -113,6 +113,13 @@ template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __f
 // one bfloat16 rounding for bf16.
 template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32<T>(from_f32<T>(v)); }
 
+// The activation of a gated feed-forward: GATED 1 = SiLU, 2 = the tanh form of GELU,
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <int GATED> __device__ __forceinline__ float gate_activation(float z) {
+    if constexpr (GATED == 2) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

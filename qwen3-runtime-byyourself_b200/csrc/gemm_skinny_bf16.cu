@@ -40,7 +40,7 @@ template <> __device__ __forceinline__ bf16 to_out<bf16>(float v) { return __flo
 // register budget is held to, so that the whole grid is resident at once for the layer sizes.
 // GATED: W holds gate and up rows interleaved in blocks of eight (rows 16t..16t+7 gate, 16t+8..
 // 16t+15 up, both for features 8t..8t+7); the kernel then writes round(silu(g)) * u, [M, N/2].
-template <int MT, int R, int WARPS, int PF, int MINB, bool GATED, typename OutT>
+template <int MT, int R, int WARPS, int PF, int MINB, int GATED, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT* __restrict__ Y, int M, int N, int K) {
     extern __shared__ __align__(16) float red[];   // [WARPS][8*MT][16*R + 1]
@@ -130,7 +130,7 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
             mine[(c + 1) * LD + n + 8] = acc[r][m][3];
         }
     __syncthreads();
-    if constexpr (!GATED) {
+    if constexpr (GATED == 0) {
         for (int idx = threadIdx.x; idx < ROWS * COLS; idx += WARPS * 32) {
             const int n = idx % ROWS, m = idx / ROWS;
             if (m >= M || n0 + n >= N) continue;
@@ -158,12 +158,12 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
             }
             g = round_to<bf16>(g);
             u = round_to<bf16>(u);
-            Y[(int64_t)m * half_n + feature] = to_out<OutT>(round_to<bf16>(g / (1.0f + expf(-g))) * u);
+            Y[(int64_t)m * half_n + feature] = to_out<OutT>(round_to<bf16>(gate_activation<GATED>(g)) * u);
         }
     }
 }
 
-template <int MT, int R, int WARPS, int PF, int MINB, bool GATED, typename OutT>
+template <int MT, int R, int WARPS, int PF, int MINB, int GATED, typename OutT>
 int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
     constexpr int SMEM = WARPS * 8 * MT * (16 * R + 1) * 4;
     static Q3PerDevice configured;
@@ -179,7 +179,7 @@ int launch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStrea
 // The shapes below come from a sweep over (rows per block, k-blocks in flight, blocks per SM, warps)
 // on the projections of an 8B-sized layer at batch 8: 16 rows of W per block always won; matrices of
 // few rows (one block per SM or less) want 16 warps sharing K, the others 8 warps and three blocks per SM.
-template <bool GATED, typename OutT>
+template <int GATED, typename OutT>
 int dispatch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || M > 64 || (GATED && N % 16 != 0)) return Q3_ERR_BAD_SIZE;
@@ -205,14 +205,21 @@ int dispatch(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, cudaStr
 }  // namespace
 
 Q3_EXPORT int q3_gemm_skinny_bf16(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
-    return dispatch<false, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
+    return dispatch<0, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
 }
 
 Q3_EXPORT int q3_gemm_skinny_bf16_f32out(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
-    return dispatch<false, float>((const bf16*)X, (const bf16*)W, (float*)Y, M, N, K, (cudaStream_t)stream);
+    return dispatch<0, float>((const bf16*)X, (const bf16*)W, (float*)Y, M, N, K, (cudaStream_t)stream);
 }
 
 // W [N, K] holds gate and up rows interleaved in blocks of eight; Y [M, N/2] = round(silu(g)) * u.
 Q3_EXPORT int q3_gemm_skinny_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, void* stream) {
-    return dispatch<true, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
+    return dispatch<1, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
+}
+
+// The same with the activation as an argument: act 1 = SiLU, 2 = the tanh form of GELU.
+Q3_EXPORT int q3_gemm_skinny_act_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int act, void* stream) {
+    if (act == 2) return dispatch<2, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
+    if (act == 1) return dispatch<1, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, (cudaStream_t)stream);
+    return Q3_ERR_BAD_SIZE;
 }

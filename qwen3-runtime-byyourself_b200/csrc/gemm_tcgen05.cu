@@ -100,7 +100,7 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v, bool
 // Grid (tiles of 128 rows of W, K ranges, tiles of MT tokens); the blocks of one tile form a cluster
 // (1, gridDim.y, 1).
 // GATED: W holds gate and up rows interleaved in blocks of eight and Y is [M, N/2] = round(silu(g)) * u.
-template <int MT, int STAGES, int MINB, bool GATED, typename OutT>
+template <int MT, int STAGES, int MINB, int GATED, typename OutT>
 __global__ void __launch_bounds__(THREADS, MINB)
 gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
@@ -222,7 +222,7 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
             const int local = (idx / GROUPS) * (int)ranks + (int)rank, g = idx % GROUPS;
             const int m = m0 + local;
             if (m >= M) continue;
-            if constexpr (!GATED) {
+            if constexpr (GATED == 0) {
                 const uint32_t addr = base + (uint32_t)(local * PART_LD + 4 * g) * 4u;
                 float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                 for (uint32_t s = 0; s < ranks; ++s) {
@@ -246,7 +246,7 @@ gemm_tcgen05_mid_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 auto gate = [](float gv, float uv) {
                     gv = round_to<bf16>(gv);
                     uv = round_to<bf16>(uv);
-                    return round_to<bf16>(gv / (1.0f + expf(-gv))) * uv;
+                    return round_to<bf16>(gate_activation<GATED>(gv)) * uv;
                 };
                 const float4 o = make_float4(gate(gs.x, us.x), gate(gs.y, us.y), gate(gs.z, us.z), gate(gs.w, us.w));
                 const int f = (n0 >> 1) + 8 * t + 4 * h;
@@ -304,11 +304,11 @@ template <> __device__ __forceinline__ void store_run8<bf16>(bf16* p, const uint
 // 32 consecutive columns (rows of W n0 + c ..) of one token's accumulator row, converted and stored; `row` points at
 // the token's first output of this tile.  GATED: the columns are gate[8] up[8] gate[8] up[8] of 16 features and
 // the output is round(silu(g)) * u with both rounded to bfloat16 first (src/ops/elementwise.cu:47-65).
-template <bool GATED, typename OutT>
+template <int GATED, typename OutT>
 __device__ __forceinline__ void store_chunk32(const uint32_t (&r)[32], OutT* row, int c, int n0, bool token_valid, int N,
                                               bool vec_ok) {
     if (!token_valid) return;
-    if constexpr (GATED) {
+    if constexpr (GATED != 0) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int n = n0 + c + h * 16;           // first gate column of this block
@@ -317,7 +317,7 @@ __device__ __forceinline__ void store_chunk32(const uint32_t (&r)[32], OutT* row
             for (int e = 0; e < 8; ++e) {
                 const float g = round_to<bf16>(__uint_as_float(r[h * 16 + e]));
                 const float u = round_to<bf16>(__uint_as_float(r[h * 16 + 8 + e]));
-                packed[e] = __float_as_uint(round_to<bf16>(g / (1.0f + expf(-g))) * u);
+                packed[e] = __float_as_uint(round_to<bf16>(gate_activation<GATED>(g)) * u);
             }
             OutT* dst = row + ((c + h * 16) >> 1);
             if (n + 16 <= N && vec_ok) {
@@ -343,7 +343,7 @@ __device__ __forceinline__ void store_chunk32(const uint32_t (&r)[32], OutT* row
     }
 }
 
-template <int BN, int STAGES, bool GATED, typename OutT>
+template <int BN, int STAGES, int GATED, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_prompt_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                            OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
@@ -687,7 +687,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int STAGES, bool GATED, typename OutT, bool QKV = false>
+template <int STAGES, int GATED, typename OutT, bool QKV = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status, const QkvEpilogue qkv) {
@@ -833,7 +833,7 @@ __device__ __forceinline__ uint32_t parked_addr(uint32_t base, int chunk, int ro
     return base + (uint32_t)chunk * SPLITK_CHUNK_BYTES + (uint32_t)(row >> 5) * 4096u + (uint32_t)quad * 512u + (uint32_t)(row & 31) * 16u;
 }
 
-template <int STAGES, bool GATED, typename OutT>
+template <int STAGES, int GATED, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                                 OutT* __restrict__ Y, int M, int N, int K, int* __restrict__ status) {
@@ -1001,7 +1001,7 @@ int mid_splits(int N, int K, int token_tiles) {
     return s;
 }
 
-template <int MT, int STAGES, int MINB, bool GATED, typename OutT>
+template <int MT, int STAGES, int MINB, int GATED, typename OutT>
 int launch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
     constexpr int RING = STAGES * (BM * BK * 2 + MT * BK * 2), PART = (MT * PART_LD * 4 + 1023) / 1024 * 1024;
     constexpr int SMEM = (RING > PART ? RING : PART) + 1024 + 256;
@@ -1022,7 +1022,7 @@ int launch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int s
 // vocabulary) wants three blocks per SM with a shorter ring, so that one block's start and end hide behind
 // the others' streams (gate/up of an 8B-sized layer at 128 rows: 41.5 us with three blocks of two stages per SM, all
 // 384 blocks resident, against 49.9 with two blocks of three stages).
-template <bool GATED, typename OutT>
+template <int GATED, typename OutT>
 int dispatch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
     const bool waves = (int64_t)((N + BM - 1) / BM) * splits > 2 * sm_count();
 #define Q3_MID(MT, ST, MB) return launch_mid<MT, ST, MB, GATED, OutT>(X, W, Y, M, N, K, splits, status, stream)
@@ -1034,7 +1034,7 @@ int dispatch_mid(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int
 #undef Q3_MID
 }
 
-template <int BN, int STAGES, bool GATED, typename OutT>
+template <int BN, int STAGES, int GATED, typename OutT>
 int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
     static Q3PerDevice configured;
@@ -1050,7 +1050,7 @@ int launch_prompt(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, in
                           map_x, map_w, Y, M, N, K, status);
 }
 
-template <int STAGES, bool GATED, typename OutT, bool QKV = false>
+template <int STAGES, int GATED, typename OutT, bool QKV = false>
 int launch_pair(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int* status, cudaStream_t stream,
                 const QkvEpilogue& qkv = QkvEpilogue{}) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
@@ -1067,7 +1067,7 @@ int launch_pair(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int*
                                   stream, dim3(2, 1, 1), map_x, map_w, Y, M, N, K, status, qkv);
 }
 
-template <int STAGES, bool GATED, typename OutT>
+template <int STAGES, int GATED, typename OutT>
 int launch_pair_splitk(const bf16* X, const bf16* W, OutT* Y, int M, int N, int K, int splits, int* status, cudaStream_t stream) {
     constexpr int SMEM = STAGES * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
     static Q3PerDevice configured;
@@ -1091,7 +1091,7 @@ int pair_capacity(int splits) {
     if (cached[dev][splits] == 0) {
         constexpr int SMEM = 6 * (BM * BK * 2 + 128 * BK * 2) + 1024 + 256;
         static Q3PerDevice configured;
-        auto kernel = gemm_tcgen05_pair_splitk_kernel<6, false, bf16>;
+        auto kernel = gemm_tcgen05_pair_splitk_kernel<6, 0, bf16>;
         if (q3_allow_shared_memory(kernel, SMEM, configured) != cudaSuccess) return 0;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * splits, 1024);
@@ -1123,16 +1123,16 @@ Q3_EXPORT int q3_gemm_tcgen05_prompt_bf16(const void* X, const void* W, void* Y,
     const bf16* x = (const bf16*)X;
     const bf16* w = (const bf16*)W;
     if (tile_n == 256)
-        return out_is_f32 ? launch_prompt<256, 4, false, float>(x, w, (float*)Y, M, N, K, status, stream)
-                          : launch_prompt<256, 4, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+        return out_is_f32 ? launch_prompt<256, 4, 0, float>(x, w, (float*)Y, M, N, K, status, stream)
+                          : launch_prompt<256, 4, 0, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
     if (tile_n == 128)
-        return out_is_f32 ? launch_prompt<128, 6, false, float>(x, w, (float*)Y, M, N, K, status, stream)
-                          : launch_prompt<128, 6, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+        return out_is_f32 ? launch_prompt<128, 6, 0, float>(x, w, (float*)Y, M, N, K, status, stream)
+                          : launch_prompt<128, 6, 0, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
     return Q3_ERR_BAD_SIZE;
 }
 
 // The prompt form on pairs of SMs: tiles of 256 tokens x 256 rows of W, each block of a pair loading half of
-// the W tile.  `gated` as below (bfloat16 output only).  `splits` (1..4) > 1: K split over that many pairs of a
+// the W tile.  `gated` as below (bfloat16 output only; 1 = SiLU, 2 = the tanh form of GELU).  `splits` (1..4) > 1: K split over that many pairs of a
 // cluster, one tile per cluster.
 Q3_EXPORT int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated,
                                         int splits, int* status, void* stream_) {
@@ -1144,13 +1144,15 @@ Q3_EXPORT int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, i
     const bf16* w = (const bf16*)W;
     if (splits > (K + BK - 1) / BK) splits = (K + BK - 1) / BK;
     if (splits > 1) {
-        if (gated) return launch_pair_splitk<6, true, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
-        return out_is_f32 ? launch_pair_splitk<6, false, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
-                          : launch_pair_splitk<6, false, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+        if (gated == 2) return launch_pair_splitk<6, 2, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+        if (gated) return launch_pair_splitk<6, 1, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+        return out_is_f32 ? launch_pair_splitk<6, 0, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
+                          : launch_pair_splitk<6, 0, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
     }
-    if (gated) return launch_pair<6, true, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
-    return out_is_f32 ? launch_pair<6, false, float>(x, w, (float*)Y, M, N, K, status, stream)
-                      : launch_pair<6, false, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+    if (gated == 2) return launch_pair<6, 2, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+    if (gated) return launch_pair<6, 1, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
+    return out_is_f32 ? launch_pair<6, 0, float>(x, w, (float*)Y, M, N, K, status, stream)
+                      : launch_pair<6, 0, bf16>(x, w, (bf16*)Y, M, N, K, status, stream);
 }
 
 // Pairs of SMs that run at once when K is split over `splits` pairs of a cluster (0: the device cannot place it).
@@ -1177,7 +1179,7 @@ Q3_EXPORT int q3_gemm_tcgen05_pair_qkv_bf16(const void* X, const void* W, int M,
     e.q_norm_w = q_norm_w; e.k_norm_w = k_norm_w; e.cos_tab = cos_tab; e.sin_tab = sin_tab;
     e.token_seq = token_seq; e.token_pos = token_pos; e.page_table = page_table;
     e.pages_per_seq = pages_per_seq; e.nq = nq; e.nkv = nkv; e.d = d; e.write_kv = write_kv; e.eps = eps;
-    return launch_pair<6, false, bf16, true>((const bf16*)X, (const bf16*)W, (bf16*)nullptr, M, (int)N, K, status,
+    return launch_pair<6, 0, bf16, true>((const bf16*)X, (const bf16*)W, (bf16*)nullptr, M, (int)N, K, status,
                                              (cudaStream_t)stream_, e);
 }
 
@@ -1187,12 +1189,12 @@ Q3_EXPORT int q3_gemm_tcgen05_prompt_gated_bf16(const void* X, const void* W, vo
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || N % 16 != 0) return Q3_ERR_BAD_SIZE;
     if (!aligned16(X) || !aligned16(W)) return Q3_ERR_MISALIGNED;
-    return launch_prompt<256, 4, true, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, status, (cudaStream_t)stream_);
+    return launch_prompt<256, 4, 1, bf16>((const bf16*)X, (const bf16*)W, (bf16*)Y, M, N, K, status, (cudaStream_t)stream_);
 }
 
 // The weights-first form for a few hundred rows of X at most (W is read once per 256 rows).  `splits` K ranges per tile of 128 rows of W (one cluster;
 // 0 = chosen from N and K).  `gated`: W [N, K] holds gate and up rows interleaved in blocks of eight and
-// Y is [M, N/2] = round(silu(g)) * u.  `status` is a device int that a kernel sets to 1/2/3 if a bounded
+// Y is [M, N/2] = round(act(g)) * u, act = SiLU (gated 1) or the tanh form of GELU (gated 2).  `status` is a device int that a kernel sets to 1/2/3 if a bounded
 // wait ran out (0 otherwise).
 Q3_EXPORT int q3_gemm_tcgen05_mid_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated,
                                        int splits, int* status, void* stream_) {
@@ -1204,11 +1206,14 @@ Q3_EXPORT int q3_gemm_tcgen05_mid_bf16(const void* X, const void* W, void* Y, in
     const bf16* w = (const bf16*)W;
     if (splits == 0) splits = mid_splits(N, K, M <= 128 ? 0 : (M + 255) / 256);
     if (splits > (K + BK - 1) / BK) splits = (K + BK - 1) / BK;
+    if (gated == 2)
+        return out_is_f32 ? dispatch_mid<2, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
+                          : dispatch_mid<2, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
     if (gated)
-        return out_is_f32 ? dispatch_mid<true, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
-                          : dispatch_mid<true, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
-    return out_is_f32 ? dispatch_mid<false, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
-                      : dispatch_mid<false, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+        return out_is_f32 ? dispatch_mid<1, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
+                          : dispatch_mid<1, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
+    return out_is_f32 ? dispatch_mid<0, float>(x, w, (float*)Y, M, N, K, splits, status, stream)
+                      : dispatch_mid<0, bf16>(x, w, (bf16*)Y, M, N, K, splits, status, stream);
 }
 
 Q3_EXPORT int q3_gemm_tcgen05_mid_splits(int N, int K, int M) { return mid_splits(N, K, M <= 128 ? 0 : (M + 255) / 256); }

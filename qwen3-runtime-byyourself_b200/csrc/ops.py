@@ -674,8 +674,9 @@ def gemm_tcgen05_mid_splits(M: int, N: int, K: int) -> int:
     return int(lib.q3_gemm_tcgen05_mid_splits(N, K, M))
 
 
-def gemm_tcgen05_mid_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int = 0) -> torch.Tensor:
-    """out[M, N/2] = round(silu(g)) * u for a few hundred rows at most; `w` [N, K] holds the gate and up rows interleaved
+def gemm_tcgen05_mid_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int = 0,
+                           activation: str = "silu") -> torch.Tensor:
+    """out[M, N/2] = round(act(g)) * u (act: SiLU or the tanh form of GELU) for a few hundred rows at most; `w` [N, K] holds the gate and up rows interleaved
     in blocks of eight (`interleave_gate_up`); the gating runs where the cluster's partial tiles are added."""
     M, K = x.shape
     N = w.shape[0]
@@ -683,21 +684,22 @@ def gemm_tcgen05_mid_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, 
         raise KernelError(f"gemm_tcgen05_mid_gated: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_mid_bf16",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K, 0, 1, int(splits),
-              _status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_mid_gated")
+    _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K, 0,
+              ACTIVATIONS[activation] + 1, int(splits), _status_word(x.device).data_ptr(), _stream()), "gemm_tcgen05_mid_gated")
     return out
 
 
-def gemm_skinny_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[M, N/2] = round(silu(g)) * u where g and u are the products of x with the gate and up rows of
-    w [N, K], which holds them interleaved in blocks of eight rows (see `interleave_gate_up`)."""
+def gemm_skinny_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """out[M, N/2] = round(act(g)) * u where g and u are the products of x with the gate and up rows of
+    w [N, K], which holds them interleaved in blocks of eight rows (see `interleave_gate_up`); act is SiLU or
+    (`activation="gelu_tanh"`) the tanh form of GELU."""
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N // 2) or N % 16 != 0 or not gemm_skinny_fits(M, K):
         raise KernelError(f"gemm_skinny_gated: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
-    fn = _fn("gemm_skinny_bf16.cu", "q3_gemm_skinny_gated_bf16", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    fn = _fn("gemm_skinny_bf16.cu", "q3_gemm_skinny_act_bf16", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out", torch.bfloat16), M, N, K,
-              _stream()), "gemm_skinny_gated")
+              ACTIVATIONS[activation] + 1, _stream()), "gemm_skinny_gated")
     return out
 
 
@@ -727,10 +729,11 @@ def gemm_tcgen05_prompt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, til
 
 
 def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False,
-                      splits: int = 1) -> torch.Tensor:
+                      splits: int = 1, activation: str = "silu") -> torch.Tensor:
     """The prompt product on pairs of SMs (tcgen05 cta_group::2): tiles of 256 tokens by 256 rows of w, each
     block of a pair loading its own tokens and half of the w tile.  `gated`: w holds gate and up rows
-    interleaved in blocks of eight and out is [M, N/2] = round(silu(g)) * u.  `splits` (1..4): K split over
+    interleaved in blocks of eight and out is [M, N/2] = round(act(g)) * u, act being SiLU or (`activation`) the tanh
+    form of GELU.  `splits` (1..4): K split over
     that many pairs of one cluster, whose partial tiles are summed over distributed shared memory in a fixed
     order (for shapes with too few tiles, or a tile count just above a whole number of waves)."""
     M, K = x.shape
@@ -744,7 +747,8 @@ def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated
     fn = _fn("gemm_tcgen05.cu", "q3_gemm_tcgen05_pair_bf16",
              [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), M, N, K,
-              int(out.dtype == torch.float32), int(gated), int(splits), _status_word(x.device).data_ptr(), _stream()),
+              int(out.dtype == torch.float32), ACTIVATIONS[activation] + 1 if gated else 0, int(splits),
+              _status_word(x.device).data_ptr(), _stream()),
            "gemm_tcgen05_pair")
     return out
 

@@ -144,6 +144,8 @@ int q3_gemm_tn_bf16(const void* X, const void* W, void* Y, int M, int N, int K, 
 int q3_gemm_skinny_bf16(const void* X, const void* W, void* Y, int M, int N, int K, void* stream);
 int q3_gemm_skinny_bf16_f32out(const void* X, const void* W, void* Y, int M, int N, int K, void* stream);
 int q3_gemm_skinny_gated_bf16(const void* X, const void* W, void* Y, int M, int N, int K, void* stream);
+/* the same with the activation as an argument: act 1 = SiLU, 2 = the tanh form of GELU */
+int q3_gemm_skinny_act_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int act, void* stream);
 /* gemm_tcgen05.cu: TMA + tcgen05; weights first with K split over a cluster (`mid`), tokens first on single SMs
    (`prompt`, tile_n 128 or 256) and on pairs of SMs (`pair`) */
 int q3_gemm_tcgen05_mid_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated, int splits,

@@ -49,14 +49,14 @@ class SwiGLU(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         N, I = ctx.n_tokens, self.intermediate_size
         act = ctx.scratch.get("ff.act", (N, I), ctx.dtype)
-        fused = self.interleaved and ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.activation == "silu"
+        fused = self.interleaved and ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
         if fused and N <= linear_module.skinny_rows:
-            ops.gemm_skinny_gated(x, self.w_gate_up, act)          # product, SiLU and gating in one kernel
+            ops.gemm_skinny_gated(x, self.w_gate_up, act, self.activation)   # product, activation and gating in one kernel
         elif fused and linear_module.tcgen05_form(N, 2 * I, self.hidden_size, gated=True) == "weights_first":
-            ops.gemm_tcgen05_mid_gated(x, self.w_gate_up, act)     # gating where the cluster's partial tiles meet
+            ops.gemm_tcgen05_mid_gated(x, self.w_gate_up, act, activation=self.activation)   # gating where the cluster's partial tiles meet
         elif fused:
             ops.gemm_tcgen05_pair(x, self.w_gate_up, act, gated=True,  # the gating runs in the product's epilogue
-                                  splits=linear_module.pair_plan(N, 2 * I, self.hidden_size)[1])
+                                  splits=linear_module.pair_plan(N, 2 * I, self.hidden_size)[1], activation=self.activation)
         else:
             gate_up = ctx.scratch.get("ff.gate_up", (N, 2 * I), ctx.dtype)
             linear(x, self.w_gate_up, gate_up)

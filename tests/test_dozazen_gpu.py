@@ -117,6 +117,42 @@ def test_gelu_gating(dtype, interleaved):
     assert np.allclose(out.double().cpu().numpy(), want, atol=1e-5 if dtype == "float32" else 3e-2, rtol=1e-5 if dtype == "float32" else 2e-2)
 
 
+@pytest.mark.parametrize("rows", [3, 40, 300])
+def test_gelu_gating_in_the_products_epilogues(rows):
+    """The gate/up product with the activation in its epilogue, in its three forms (few rows, weights first, pairs of
+    SMs), against the plain product: both sums rounded to bfloat16, then round(gelu(g)) * u."""
+    import torch
+    from qwen3_b200.csrc import ops
+    rng = np.random.default_rng(rows)
+    K, inter = 128, 256
+    x = torch.tensor(rng.standard_normal((rows, K)), dtype=torch.bfloat16, device="cuda")
+    gate = torch.tensor(rng.standard_normal((inter, K)) / 8, dtype=torch.bfloat16, device="cuda")
+    up = torch.tensor(rng.standard_normal((inter, K)) / 8, dtype=torch.bfloat16, device="cuda")
+    w = ops.interleave_gate_up(gate, up)
+    xd = x.double().cpu().numpy()
+    g = plain.round_bf16(xd @ gate.double().cpu().numpy().T)
+    u = plain.round_bf16(xd @ up.double().cpu().numpy().T)
+    want = plain.round_bf16(plain.gelu_tanh(g)) * u
+    out = torch.empty((rows, inter), dtype=torch.bfloat16, device="cuda")
+    if rows <= 8:
+        ops.gemm_skinny_gated(x, w, out, "gelu_tanh")
+    elif rows <= 128:
+        ops.gemm_tcgen05_mid_gated(x, w, out, activation="gelu_tanh")
+    else:
+        ops.gemm_tcgen05_pair(x, w, out, gated=True, activation="gelu_tanh")
+    err = np.abs(out.double().cpu().numpy() - want)
+    assert float(err.max()) <= 0.03 + 0.02 * float(np.abs(want).max()), float(err.max())
+    silu = torch.empty_like(out)                                   # the default stays SiLU
+    if rows <= 8:
+        ops.gemm_skinny_gated(x, w, silu)
+    elif rows <= 128:
+        ops.gemm_tcgen05_mid_gated(x, w, silu)
+    else:
+        ops.gemm_tcgen05_pair(x, w, silu, gated=True)
+    want_silu = plain.round_bf16(g / (1 + np.exp(-g))) * u
+    assert float(np.abs(silu.double().cpu().numpy() - want_silu).max()) <= 0.03 + 0.02 * float(np.abs(want_silu).max())
+
+
 # ---------------------------------------------------------------------------- attention over pages
 class Paged:
     """Keys and values of a few sequences in pages that lie in no particular order, as the kernels read them."""
