@@ -351,7 +351,7 @@ def design_configs(width, heads, kv, d, ff, layers, chunk):
                "logit_scale": 1.0, "logit_softcap": 30.0, "loop": {"start": 0, "stop": layers, "times": 1},
                "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}} for _ in range(layers)]}
     qwen3 = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
-                 head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB)
+                 head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB, bos_token_id=1, eos_token_id=2)
     return dozazen, qwen3
 
 

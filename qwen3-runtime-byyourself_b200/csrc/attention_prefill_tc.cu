@@ -19,6 +19,14 @@
 //              P as packed bfloat16 into TMEM columns [64,96), and at the end normalises O
 // Every mbarrier wait is bounded and reports into `status`.  Head sizes 64 and 128, no window;
 // other shapes use the mma.sync kernel of attention_prefill.cu.
+//
+// Compiled with -DQ3_CAPPED=1 the same kernel serves mixers with capped scores, chunks and a sink
+// (its entry point is then q3_attention_capped_prefill_tc_bf16):
+//   s <- cap * tanh(dot * scale / cap) (cap 0: dot * scale), with tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1) on the
+//   special-function unit; a query sees the keys of its own chunk of `chunk` positions only (0: all before it),
+//   so a tile's pages start at the page of its first row's chunk start; with a sink the running maximum
+//   starts at 0 and the running sum at the sink's weight.  The softmax and its weights are computed in 32-bit;
+//   the weights enter the second product rounded to bfloat16, as the operands of every product are.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -29,7 +37,20 @@
 #error "compile with -DQ3_HEAD_DIM=<64 or 128>"
 #endif
 
+#ifndef Q3_CAPPED
+#define Q3_CAPPED 0
+#endif
+
 namespace {
+
+constexpr bool CAPPED = Q3_CAPPED != 0;
+// What the capped form needs beyond the plain one's arguments (all zero in the plain form).
+struct CapArgs {
+    float scale;       // of the raw dot
+    float cap;         // 0: no cap
+    int chunk;         // 0: every earlier key is seen
+    int sink;          // 1: one more term exp(0) in the denominator
+};
 
 constexpr int D = Q3_HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 attention takes head sizes 64 and 128");
@@ -100,6 +121,11 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
     asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -115,7 +141,7 @@ __global__ void __launch_bounds__(THREADS)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ seq_start,
                   const int* __restrict__ seq_pos0, const int* __restrict__ page_table, int pages_per_seq, int n_seqs,
-                  int n_tiles, int nq, int nkv, float scale_log2, int* __restrict__ status) {
+                  int n_tiles, int nq, int nkv, float scale_log2, int* __restrict__ status, const CapArgs capped) {
     extern __shared__ unsigned char smem_raw[];
     pdl_launch_dependents();
     pdl_wait();
@@ -132,7 +158,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int* pages = page_table + (int64_t)seq * pages_per_seq;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rows = min(BM, n_new - tile * BM);
-    const int n_pages = (pos0 + tile * BM + rows - 1) / PAGE + 1;        // pages 0 .. the one of the last row
+    // pages first_page .. the one of the last row (first_page: where the chunk of the tile's first row starts)
+    const int first_page = (CAPPED && capped.chunk > 0) ? ((pos0 + tile * BM) / capped.chunk * capped.chunk) / PAGE : 0;
+    const int n_pages = (pos0 + tile * BM + rows - 1) / PAGE + 1 - first_page;
 
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {                                  // the swizzled tiles need 1024-byte alignment
@@ -182,7 +210,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const int s = j % K_STAGES;
                 if (!mbar_wait(bar_k_empty + 8 * s, ((uint32_t)(j / K_STAGES) & 1u) ^ 1u)) { atomicExch(status, 11); break; }
                 const uint32_t dst = k_smem + s * PANEL_BYTES;
-                const int row = (pages[j] * nkv + kvh) * PAGE;
+                const int row = (pages[first_page + j] * nkv + kvh) * PAGE;
                 mbar_expect_tx(bar_k_full + 8 * s, PANEL_BYTES);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * PAGE * 128, &map_k, bar_k_full + 8 * s, h * 64, row);
@@ -195,7 +223,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const int s = j % V_STAGES;
                 if (!mbar_wait(bar_v_empty + 8 * s, ((uint32_t)(j / V_STAGES) & 1u) ^ 1u)) { atomicExch(status, 19); break; }
                 const uint32_t dst = v_smem + s * PANEL_BYTES;
-                const int row = (pages[j] * nkv + kvh) * PAGE;
+                const int row = (pages[first_page + j] * nkv + kvh) * PAGE;
                 mbar_expect_tx(bar_v_full + 8 * s, PANEL_BYTES);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) tma_load_2d(dst + h * PAGE * 128, &map_v, bar_v_full + 8 * s, h * 64, row);
@@ -251,6 +279,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         const uint32_t t_row = tmem + ((uint32_t)lane_base << 16);
         float m_run = -INFINITY, l_run = 0.0f;
         bool ok = true;
+        // the capped form: the first key this row sees, and the constants of s -> cap * tanh(s * scale / cap) in log2 units
+        const int c_row = (CAPPED && capped.chunk > 0) ? p_row / capped.chunk * capped.chunk : 0;
+        const int c_last = (CAPPED && capped.chunk > 0) ? (pos0 + tile * BM + BM - 1) / capped.chunk * capped.chunk : 0;
+        const float cap_l2 = capped.cap * 1.4426950408889634f;                       // the cap in log2 units
+        const float tanh_k = capped.cap > 0.0f ? 2.0f * capped.scale * 1.4426950408889634f / capped.cap : 0.0f;
         for (int j = 0; j < n_pages && ok; ++j) {
             ok = mbar_wait(bar_s_full, (uint32_t)j & 1u);
             if (!ok) { if (lane == 0) atomicExch(status, 15); break; }
@@ -262,12 +295,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_s_read);
-            const int key0 = j * PAGE;
-            const bool edge = key0 + PAGE - 1 > pos0 + tile * BM;           // some key of the page lies after some row
+            const int key0 = (first_page + j) * PAGE;
+            // some key of the page lies after some row (or, with chunks, before the chunk of some row)
+            const bool edge = key0 + PAGE - 1 > pos0 + tile * BM || (CAPPED && key0 < c_last);
             if (edge) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c)
-                    if (key0 + c > p_row) s[c] = 0xff800000u;                // -inf
+                    if (key0 + c > p_row || (CAPPED && key0 + c < c_row)) s[c] = 0xff800000u;                // -inf
             }
             // the page's maximum on the raw dots (the scale is positive), four chains side by side
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -276,11 +310,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
                 for (int e = 0; e < 4; ++e) mx[e] = max3(mx[e], __uint_as_float(s[c + e]), __uint_as_float(s[c + 4 + e]));
             }
-            const float m_page = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+            float m_page = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            if (CAPPED && capped.cap > 0.0f) {          // the cap is monotonic: the maximum of the capped scores is the capped maximum
+                if (m_page != -INFINITY) m_page = cap_l2 * (1.0f - 2.0f * rcp_approx(ex2_approx(m_page * tanh_k) + 1.0f));
+            } else {
+                m_page *= scale_log2;
+            }
             float alpha = 1.0f;
             bool raise = false;
             if (j == 0) {
-                m_run = m_page == -INFINITY ? 0.0f : m_page;                 // the first page overwrites O: nothing to rescale
+                if (CAPPED) {
+                    // a row may see nothing of its tile's first page (its chunk starts later): a maximum below every
+                    // score then lets the next page raise it; the sink is a key of score 0 that is always seen
+                    m_run = capped.sink ? fmaxf(m_page, 0.0f) : (m_page == -INFINITY ? -1.0e30f : m_page);
+                    l_run = capped.sink ? ex2_approx(-m_run) : 0.0f;
+                } else {
+                    m_run = m_page == -INFINITY ? 0.0f : m_page;             // the first page overwrites O: nothing to rescale
+                }
             } else if (m_page > m_run + RESCALE_THRESHOLD) {
                 alpha = ex2_approx(m_run - m_page);
                 m_run = m_page;
@@ -292,11 +338,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(neg_m, neg_m);
             uint64_t part2[2] = {pack_f32x2(0.0f, 0.0f), pack_f32x2(0.0f, 0.0f)};
             uint32_t p[32];
+            // the capped form: x = cap_l2 * (1 - 2 / (2^(dot * tanh_k) + 1)) - m = -2 cap_l2 / (...) + (cap_l2 - m)
+            const uint64_t tanh_k2 = pack_f32x2(tanh_k, tanh_k), one2 = pack_f32x2(1.0f, 1.0f);
+            const uint64_t slope2 = pack_f32x2(-2.0f * cap_l2, -2.0f * cap_l2), shift2 = pack_f32x2(cap_l2 + neg_m, cap_l2 + neg_m);
+            const bool use_cap = CAPPED && capped.cap > 0.0f;
 #pragma unroll
             for (int c = 0; c < 64; c += 4) {
                 float x0, x1, x2, x3;
-                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, neg_m2), x0, x1);
-                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), scale2, neg_m2), x2, x3);
+                if (use_cap) {
+                    float t0, t1, t2, t3;
+                    unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), tanh_k2), t0, t1);
+                    unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), tanh_k2), t2, t3);
+                    unpack_f32x2(add_f32x2(pack_f32x2(ex2_approx(t0), ex2_approx(t1)), one2), t0, t1);
+                    unpack_f32x2(add_f32x2(pack_f32x2(ex2_approx(t2), ex2_approx(t3)), one2), t2, t3);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(rcp_approx(t0), rcp_approx(t1)), slope2, shift2), x0, x1);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(rcp_approx(t2), rcp_approx(t3)), slope2, shift2), x2, x3);
+                    if (edge) {                          // a key that is not seen has a capped score too: take it out again
+                        if (s[c] == 0xff800000u) x0 = -INFINITY;
+                        if (s[c + 1] == 0xff800000u) x1 = -INFINITY;
+                        if (s[c + 2] == 0xff800000u) x2 = -INFINITY;
+                        if (s[c + 3] == 0xff800000u) x3 = -INFINITY;
+                    }
+                } else {
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), scale2, neg_m2), x0, x1);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), scale2, neg_m2), x2, x3);
+                }
                 const float a = ex2_approx(x0), b = ex2_approx(x1), e = ex2_approx(x2), f = ex2_approx(x3);
                 part2[0] = add_f32x2(part2[0], pack_f32x2(a, b));
                 part2[1] = add_f32x2(part2[1], pack_f32x2(e, f));
@@ -375,11 +441,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
 Q3_EXPORT int q3_attention_prefill_tc_head_dim() { return D; }
 
-// q: [n_tokens, nq * D]; k_pages, v_pages: [n_cache_pages, nkv, 64, D]; out: [n_tokens, nq * D].
-Q3_EXPORT int q3_attention_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
-                                           const int* seq_start, const int* seq_pos0, const int* page_table,
-                                           int pages_per_seq, int n_seqs, int max_new, int64_t n_tokens,
-                                           int64_t n_cache_pages, int nq, int nkv, float scale, int* status, void* stream) {
+static int launch_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_start,
+                             const int* seq_pos0, const int* page_table, int pages_per_seq, int n_seqs, int max_new,
+                             int64_t n_tokens, int64_t n_cache_pages, int nq, int nkv, float scale, int* status, void* stream,
+                             CapArgs capped) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || !(scale > 0.0f)) return Q3_ERR_BAD_SIZE;   // the row maximum is taken before scaling
     if (n_seqs > 65535 || nq > 65535) return Q3_ERR_TOO_LARGE;
@@ -398,5 +463,30 @@ Q3_EXPORT int q3_attention_prefill_tc_bf16(const void* q, const void* k_pages, c
     if (blocks > 0x7fffffff) return Q3_ERR_TOO_LARGE;
     return (int)q3_launch(prefill_tc_kernel, dim3((unsigned)blocks), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, map_q,
                           map_k, map_v, (bf16*)out, seq_start, seq_pos0, page_table, pages_per_seq, n_seqs, n_tiles, nq, nkv,
-                          scale * 1.4426950408889634f, status);
+                          scale * 1.4426950408889634f, status, capped);
 }
+
+#if Q3_CAPPED
+// The capped form: softcap >= 0 (0: none), chunk >= 0 (0: none), sink 0 or 1; otherwise as below.
+Q3_EXPORT int q3_attention_capped_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                                  const int* seq_start, const int* seq_pos0, const int* page_table,
+                                                  int pages_per_seq, int n_seqs, int max_new, int64_t n_tokens,
+                                                  int64_t n_cache_pages, int nq, int nkv, float scale, float softcap, int chunk,
+                                                  int sink, int* status, void* stream) {
+    if (softcap < 0.0f || chunk < 0) return Q3_ERR_BAD_SIZE;
+    CapArgs capped;
+    capped.scale = scale; capped.cap = softcap; capped.chunk = chunk; capped.sink = sink ? 1 : 0;
+    return launch_prefill_tc(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, pages_per_seq, n_seqs, max_new, n_tokens,
+                             n_cache_pages, nq, nkv, scale, status, stream, capped);
+}
+#else
+// q: [n_tokens, nq * D]; k_pages, v_pages: [n_cache_pages, nkv, 64, D]; out: [n_tokens, nq * D].
+Q3_EXPORT int q3_attention_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const int* seq_start, const int* seq_pos0, const int* page_table,
+                                           int pages_per_seq, int n_seqs, int max_new, int64_t n_tokens,
+                                           int64_t n_cache_pages, int nq, int nkv, float scale, int* status, void* stream) {
+    CapArgs capped = {};
+    return launch_prefill_tc(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, pages_per_seq, n_seqs, max_new, n_tokens,
+                             n_cache_pages, nq, nkv, scale, status, stream, capped);
+}
+#endif

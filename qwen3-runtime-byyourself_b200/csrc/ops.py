@@ -487,6 +487,28 @@ def attention_capped_decode(q, k_pages, v_pages, out, scratch, token_seq, token_
     return out
 
 
+def attention_capped_prefill_tc_fits(d: int, vd: int, window: Optional[int]) -> bool:
+    return d in (64, 128) and vd == d and not window
+
+
+def attention_capped_prefill_tc(q, k_pages, v_pages, out, seq_start, seq_pos0, page_table, n_seqs: int, max_new: int,
+                                n_tokens: int, nq: int, nkv: int, d: int, scale: float, softcap: float = 0.0,
+                                chunk: Optional[int] = None, sink: bool = False):
+    """`attention_capped_prefill` with both products on tcgen05 (TMA-fed, scores and output in tensor memory): head
+    sizes 64 and 128, values as wide as keys."""
+    if q.dtype != torch.bfloat16 or not attention_capped_prefill_tc_fits(d, d, None) or not scale > 0:
+        raise KernelError("attention_capped_prefill_tc: bfloat16, head size 64 or 128, a positive scale")
+    fn = _fn("attention_prefill_tc.cu", "q3_attention_capped_prefill_tc_bf16",
+             [c_void_p] * 7 + [c_int, c_int, c_int, c_int64, c_int64, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p],
+             defines=(f"Q3_HEAD_DIM={d}", "Q3_CAPPED=1"))
+    _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
+              _dev(out, "out", torch.bfloat16), _dev(seq_start, "seq_start", torch.int32),
+              _dev(seq_pos0, "seq_pos0", torch.int32), _dev(page_table, "page_table", torch.int32),
+              page_table.shape[-1], n_seqs, max_new, n_tokens, k_pages.shape[0], nq, nkv, float(scale), float(softcap or 0.0),
+              int(chunk or 0), int(bool(sink)), _status_word(q.device).data_ptr(), _stream()), "attention_capped_prefill_tc")
+    return out
+
+
 # ------------------------------------------------------------------ sampling
 def argmax(logits: torch.Tensor, out: torch.Tensor, valid: Optional[int] = None) -> torch.Tensor:
     """out[r] = index of the highest logit of row r (lowest id among equals, NaN as -inf)."""

@@ -95,6 +95,13 @@ int q3_attention_generic_bf16(const void* q, const void* k_pages, const void* v_
                               const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
                               float scale, int window, int value_dim, float softcap, int chunk, int sink, void* stream);
 
+/* attention_prefill_tc.cu compiled with -DQ3_CAPPED=1: the tcgen05 prompt attention with capped scores, chunks and a sink
+   (head sizes 64 and 128, values as wide as keys); arguments as q3_attention_prefill_tc_bf16 plus softcap, chunk, sink */
+int q3_attention_capped_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_start,
+                                        const int* seq_pos0, const int* page_table, int pages_per_seq, int n_seqs, int max_new,
+                                        int64_t n_tokens, int64_t n_cache_pages, int nq, int nkv, float scale, float softcap, int chunk,
+                                        int sink, int* status, void* stream);
+
 /* ---- attention_capped.cu (-DQ3_HEAD_DIM, -DQ3_VALUE_DIM): bfloat16 attention with scores capped by softcap * tanh(s / softcap)
    (0: none), chunked visibility (chunk 0: causal only), a sink term in the softmax's denominator, values of their own size */
 int q3_attention_capped_head_dim(void);

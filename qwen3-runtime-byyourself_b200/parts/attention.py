@@ -286,6 +286,18 @@ def _prefill_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     return True
 
 
+def _prefill_capped_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
+    """The same on tcgen05 with TMA-fed tiles: head sizes 64 and 128, values as wide as keys, and enough new tokens
+    for 128-row tiles to be worth it."""
+    if part.plain or not ops.attention_capped_prefill_tc_fits(part.head_dim, part.value_dim, part.window) \
+            or ctx.max_new < tc_prefill_rows or part.scale <= 0:
+        return False
+    ops.attention_capped_prefill_tc(q[:ctx.n_tokens], cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table,
+                                    ctx.n_seqs, ctx.max_new, ctx.n_tokens, part.num_heads, part.num_kv_heads, part.head_dim,
+                                    part.scale, part.softcap, part.chunk, part.sink)
+    return True
+
+
 def _decode_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     """The same for decode steps: split over the keys of the chunk (or of the whole context), merged with the sink."""
     nq, nkv = part.num_heads, part.num_kv_heads
@@ -311,6 +323,7 @@ FUSED_DECODE_KERNELS.append(_decode_fused_kernel)
 FUSED_PROJECTION_KERNELS.append(_projection_pair_kernel)
 PREFILL_KERNELS.append(_prefill_tcgen05_kernel)
 PREFILL_KERNELS.append(_prefill_flash_kernel)
+PREFILL_KERNELS.append(_prefill_capped_tcgen05_kernel)
 PREFILL_KERNELS.append(_prefill_capped_kernel)
 DECODE_KERNELS.append(_decode_capped_kernel)
 

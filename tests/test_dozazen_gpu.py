@@ -204,7 +204,8 @@ class Paged:
 def attention_cases():
     # (query heads, kv heads, d, vd, scale, softcap, chunk, sink)
     return [(4, 2, 32, 16, 0.3, 8.0, 40, True), (6, 1, 24, 20, 0.25, 0.0, 96, True), (2, 2, 64, 64, 0.125, 30.0, 64, True),
-            (8, 2, 64, 32, 0.2, 15.0, 200, True), (3, 3, 16, 48, 0.5, 5.0, 0, True), (4, 1, 128, 128, 0.09, 20.0, 128, False)]
+            (8, 2, 64, 32, 0.2, 15.0, 200, True), (3, 3, 16, 48, 0.5, 5.0, 0, True), (4, 1, 128, 128, 0.09, 20.0, 128, False),
+            (4, 2, 128, 128, 0.09, 25.0, 100, True), (2, 1, 64, 64, 0.125, 0.0, 0, True), (2, 2, 64, 64, 0.125, 10.0, 72, False)]
 
 
 def edge_positions(n, chunk):
@@ -306,6 +307,13 @@ def test_tensor_core_attention_over_pages_at_every_edge(nq, nkv, d, vd, scale, c
         ops.attention_capped_prefill(q.cuda().view(len(tokens), nq * d).contiguous(), paged.k_pages, paged.v_pages, out, seq_start,
                                      pos0, table, len(lengths), max(counts), nq, nkv, d, vd, scale, cap, chunk or None, sink)
         compare(out, q, tokens, f"prompt from {starts}")
+        if ops.attention_capped_prefill_tc_fits(d, vd, None):          # the same on tcgen05
+            out.fill_(7.0)
+            ops.attention_capped_prefill_tc(q.cuda().view(len(tokens), nq * d).contiguous(), paged.k_pages, paged.v_pages, out,
+                                            seq_start, pos0, table, len(lengths), max(counts), len(tokens), nq, nkv, d, scale, cap,
+                                            chunk or None, sink)
+            assert ops.tcgen05_status(out.device) == 0
+            compare(out, q, tokens, f"tcgen05 prompt from {starts}")
 
     prompt([0, 0, 0])
     c = chunk or 64
