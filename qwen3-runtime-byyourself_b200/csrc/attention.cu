@@ -164,7 +164,7 @@ __global__ void qkv_prepare_vec_kernel(const T* __restrict__ qkv, T* __restrict_
                                        const float* __restrict__ sin_tab, const int* __restrict__ token_seq,
                                        const int* __restrict__ token_pos, const int* __restrict__ page_table,
                                        int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv,
-                                       int64_t n_tokens) {
+                                       int64_t n_tokens, const float* __restrict__ bias) {
     constexpr int VEC = Pack<T>::N;
     pdl_launch_dependents();
     pdl_wait();
@@ -186,6 +186,14 @@ __global__ void qkv_prepare_vec_kernel(const T* __restrict__ qkv, T* __restrict_
     if (live) {
         load_pack_f32<T>(src, a);
         load_pack_f32<T>(src + half, b);
+        if (bias != nullptr) {                       // one value per column of the projection, added before anything else
+            const float* bh = bias + (int64_t)head * d + sub * VEC;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                a[i] = round_to<T>(a[i] + bh[i]);
+                b[i] = round_to<T>(b[i] + bh[half + i]);
+            }
+        }
     }
     const float* norm_w = is_q ? q_norm_w : (is_v ? nullptr : k_norm_w);
     // the sum over the lanes of a head: every lane of the warp takes part in every shuffle
@@ -302,7 +310,7 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
     if (vd <= 0) vd = d;                         // values as wide as keys
     if (vd > MAX_HEAD_DIM) return Q3_ERR_BAD_SIZE;
     constexpr int VEC = Pack<T>::N;
-    if (rot == d && bias == nullptr && vd == d && n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
+    if (rot == d && vd == d && n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
         aligned16(k_pages) && aligned16(v_pages)) {
         const int hpw = 32 / ((d / 2) / VEC);
         const int64_t n_warps = (n_tokens * (nq + 2 * nkv) + hpw - 1) / hpw;
@@ -310,7 +318,7 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
         if (blocks > 0x7fffffffLL) return Q3_ERR_TOO_LARGE;
         return (int)q3_launch(qkv_prepare_vec_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, qkv, q_out, k_pages,
                               v_pages, q_norm_w, k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq,
-                              nq, nkv, d, eps, write_kv, n_tokens);
+                              nq, nkv, d, eps, write_kv, n_tokens, bias);
     }
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const int warps = 4;

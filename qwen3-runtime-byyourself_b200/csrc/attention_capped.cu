@@ -20,7 +20,10 @@
 //            a block takes a range of the pages between the chunk's start and the token, each of its four
 //            warps 16 keys of every page through its own cp.async pipeline; partial results (sums, maximum,
 //            denominator) go to a float32 scratch and a second small kernel merges the splits, adds the sink
-//            and divides.
+//            and divides.  The fused form takes the output of the q/k/v projection as it is: every block adds
+//            the bias to the group's query heads and rotates them itself, and the block that holds the token's
+//            own page does the same for the new key and value, writes them into the cache and adds their term
+//            to its partial result directly (the page was asked for before they were written).
 // Compiled for one pair of sizes: -DQ3_HEAD_DIM=<keys> -DQ3_VALUE_DIM=<values>, multiples of 16 up to 256.
 #include "common.cuh"
 
@@ -265,12 +268,52 @@ constexpr int DECODE_PIPE = WARPS * STAGES * (K_PANEL + V_PANEL);
 constexpr int DECODE_MERGE = WARPS * 16 * (VD + 2) * 4;
 constexpr int DECODE_SMEM = DECODE_PIPE > DECODE_MERGE ? DECODE_PIPE : DECODE_MERGE;
 
+// the fused form keeps, behind the pipeline: the prepared queries [16][D], the new key [D] and value [VD] (bf16) and
+// the new key's scores [16] (float32)
+constexpr int DECODE_PREP = (16 * D + D + VD) * 2 + 16 * 4;
+constexpr int DECODE_SMEM_FUSED = DECODE_SMEM + DECODE_PREP;
+
+// What the fused form needs beyond the split form's arguments.
+struct FusedArgs {
+    const bf16* qkv;               // [tokens, (nq + nkv) * D + nkv * VD]: the projection output as it is
+    const float* bias;             // one value per column of it, or null
+    const float* cos_tab;          // [positions, rot / 2] or null
+    const float* sin_tab;
+    int rot;                       // the first `rot` values of a query or key head are rotated in pairs (i, i + rot/2)
+};
+
+// One head of the projection output with its bias added and (if `cos_tab`) rotated, by one warp, exactly as
+// qkv_prepare does it (attention.cu), so that the cache holds the same values whichever kernel wrote them.
+template <int SIZE>
+__device__ __forceinline__ void prepare_head(const bf16* __restrict__ src, const float* __restrict__ bias, bf16* dst,
+                                             const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int pos,
+                                             int rot, int lane) {
+    const int rhalf = cos_tab != nullptr ? rot >> 1 : 0;
+    for (int i = lane; i < rhalf; i += 32) {
+        float a = __bfloat162float(src[i]), b = __bfloat162float(src[i + rhalf]);
+        if (bias != nullptr) {
+            a = round_to<bf16>(a + bias[i]);
+            b = round_to<bf16>(b + bias[i + rhalf]);
+        }
+        const float cs = cos_tab[(int64_t)pos * rhalf + i], sn = sin_tab[(int64_t)pos * rhalf + i];
+        dst[i] = __float2bfloat16_rn(a * cs - b * sn);
+        dst[i + rhalf] = __float2bfloat16_rn(b * cs + a * sn);
+    }
+    for (int i = 2 * rhalf + lane; i < SIZE; i += 32) {
+        float c = __bfloat162float(src[i]);
+        if (bias != nullptr) c = round_to<bf16>(c + bias[i]);
+        dst[i] = __float2bfloat16_rn(c);
+    }
+}
+
 // part: [tokens, nq, splits, VD + 2] float32: the unnormalised sums, then the maximum (base-2 scale) and the denominator.
+// FUSED: `q` is unused; the pages are written by the block that holds the token's own page.
+template <bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32)
-decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, const bf16* v_pages,
                            float* __restrict__ part, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                            const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, float scale, float cap,
-                           int chunk) {
+                           int chunk, const FusedArgs fused) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -300,10 +343,51 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) issue(s);
 
+    // the block that holds the token's own page owns the new key and value
+    const bool owner = FUSED && count > 0 && pg_end == first_page + n_pages;
+    bf16* prep_q = reinterpret_cast<bf16*>(smem + DECODE_SMEM);          // [16][D]
+    bf16* new_k = prep_q + 16 * D;                                       // [D]
+    bf16* new_v = new_k + D;                                             // [VD]
+    float* new_s = reinterpret_cast<float*>(new_v + VD);                 // [16]: the new key's scores, base-2 scale
+    if constexpr (FUSED) {
+        const int64_t width = (int64_t)(nq + nkv) * D + (int64_t)nkv * VD;
+        const bf16* row = fused.qkv + (int64_t)t * width;
+        for (int r = warp; r < G; r += WARPS) {
+            const int64_t col = (int64_t)(kvh * G + r) * D;
+            prepare_head<D>(row + col, fused.bias ? fused.bias + col : nullptr, prep_q + r * D, fused.cos_tab, fused.sin_tab, pos,
+                            fused.rot, lane);
+        }
+        if (owner) {
+            if (warp == G % WARPS) {
+                const int64_t col = (int64_t)(nq + kvh) * D;
+                prepare_head<D>(row + col, fused.bias ? fused.bias + col : nullptr, new_k, fused.cos_tab, fused.sin_tab, pos,
+                                fused.rot, lane);
+            }
+            if (warp == (G + 1) % WARPS) {
+                const int64_t col = (int64_t)(nq + nkv) * D + (int64_t)kvh * VD;
+                prepare_head<VD>(row + col, fused.bias ? fused.bias + col : nullptr, new_v, nullptr, nullptr, pos, 0, lane);
+            }
+        }
+        __syncthreads();
+        if (owner) {       // into the cache for the steps to come; this step takes them from shared memory
+            const int64_t at = ((int64_t)pages[pos / PAGE] * nkv + kvh) * PAGE + pos % PAGE;
+            for (int i = threadIdx.x; i < D; i += WARPS * 32) const_cast<bf16*>(k_pages)[at * D + i] = new_k[i];
+            for (int i = threadIdx.x; i < VD; i += WARPS * 32) const_cast<bf16*>(v_pages)[at * VD + i] = new_v[i];
+            for (int r = warp; r < G; r += WARPS) {                      // q.k of the new key, as the tensor core would sum it
+                float dot = 0.0f;
+                for (int i = lane; i < D; i += 32) dot = fmaf(__bfloat162float(prep_q[r * D + i]), __bfloat162float(new_k[i]), dot);
+                dot = warp_sum(dot);
+                if (lane == 0) new_s[r] = score_log2(dot, scale, cap, inv_cap);
+            }
+        }
+    }
+    // in the fused form the token's own key is not in the page that was asked for: it is added at the merge
+    const int last_key = FUSED ? pos - 1 : pos;
+
     // query rows of the group as A fragments: row r = head kvh*G + r (rows >= G are zero)
     uint32_t qa[KT][4];
     {
-        const bf16* q0 = q + ((int64_t)t * nq + (int64_t)kvh * G) * D;
+        const bf16* q0 = FUSED ? prep_q : q + ((int64_t)t * nq + (int64_t)kvh * G) * D;
 #pragma unroll
         for (int kt = 0; kt < KT; ++kt) {
             const int c = kt * 16 + tq * 2;
@@ -340,7 +424,7 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + j * 8 + (e & 1);
-                const float v = (key >= lo && key <= pos) ? score_log2(s[j][e], scale, cap, inv_cap) : -INFINITY;
+                const float v = (key >= lo && key <= last_key) ? score_log2(s[j][e], scale, cap, inv_cap) : -INFINITY;
                 s[j][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -411,7 +495,7 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * VD; idx += WARPS * 32) {
         const int row = idx / VD, c = idx % VD;
-        float m = -INFINITY;
+        float m = owner ? new_s[row] : -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sm_ml[(w * 16 + row) * 2]);
         float acc = 0.0f, l = 0.0f;
@@ -421,6 +505,11 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ 
             const float f = mw == -INFINITY ? 0.0f : exp2f(mw - m);
             acc += f * sm_o[(w * 16 + row) * VD + c];
             l += f * sm_ml[(w * 16 + row) * 2 + 1];
+        }
+        if (owner) {                                   // the token's own key and value: one more term
+            const float f = exp2f(new_s[row] - m);
+            acc += f * __bfloat162float(new_v[c]);
+            l += f;
         }
         float* dst = part + (((int64_t)t * nq + kvh * G + row) * n_splits + split) * (VD + 2);
         dst[c] = acc;
@@ -490,12 +579,41 @@ Q3_EXPORT int q3_attention_capped_decode_bf16(const void* q, const void* k_pages
     if (n_tokens > 65535 || nkv > 65535 || nq > 0x7fffffff / 2) return Q3_ERR_TOO_LARGE;
     static Q3PerDevice configured;
     {
-        cudaError_t e = q3_allow_shared_memory(decode_capped_split_kernel, DECODE_SMEM, configured);
+        cudaError_t e = q3_allow_shared_memory(decode_capped_split_kernel<false>, DECODE_SMEM, configured);
         if (e != cudaSuccess) return (int)e;
     }
-    cudaError_t e = q3_launch(decode_capped_split_kernel, dim3(n_splits, nkv, (unsigned)n_tokens), dim3(WARPS * 32), DECODE_SMEM,
+    FusedArgs none = {};
+    cudaError_t e = q3_launch(decode_capped_split_kernel<false>, dim3(n_splits, nkv, (unsigned)n_tokens), dim3(WARPS * 32), DECODE_SMEM,
                               (cudaStream_t)stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, scratch, token_seq,
-                              token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk);
+                              token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, none);
+    if (e != cudaSuccess) return (int)e;
+    return (int)q3_launch(decode_capped_merge_kernel, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
+                          (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink);
+}
+
+// The same from the output of the q/k/v projection as it is, qkv [tokens, (nq + nkv) * D + nkv * VD]: the bias (may be null),
+// the rotation of the first rotary_dim values of the query and key heads (tables [positions, rotary_dim / 2], may be null) and
+// the write of the new key and value into their pages happen in the attention's own kernel.
+Q3_EXPORT int q3_attention_capped_decode_fused_bf16(const void* qkv, void* k_pages, void* v_pages, void* out, float* scratch,
+                                                    const float* bias, const float* cos_tab, const float* sin_tab, int rotary_dim,
+                                                    const int* token_seq, const int* token_pos, const int* page_table,
+                                                    int pages_per_seq, int64_t n_tokens, int nq, int nkv, float scale,
+                                                    float softcap, int chunk, int sink, int n_splits, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || softcap < 0.0f || chunk < 0 || n_splits <= 0) return Q3_ERR_BAD_SIZE;
+    if ((cos_tab == nullptr) != (sin_tab == nullptr) || rotary_dim < 0 || rotary_dim % 2 != 0 || rotary_dim > D) return Q3_ERR_BAD_SIZE;
+    if (n_tokens > 65535 || nkv > 65535 || nq > 0x7fffffff / 2) return Q3_ERR_TOO_LARGE;
+    static Q3PerDevice configured;
+    {
+        cudaError_t e = q3_allow_shared_memory(decode_capped_split_kernel<true>, DECODE_SMEM_FUSED, configured);
+        if (e != cudaSuccess) return (int)e;
+    }
+    FusedArgs fused;
+    fused.qkv = (const bf16*)qkv; fused.bias = bias; fused.cos_tab = cos_tab; fused.sin_tab = sin_tab;
+    fused.rot = rotary_dim > 0 ? rotary_dim : D;
+    cudaError_t e = q3_launch(decode_capped_split_kernel<true>, dim3(n_splits, nkv, (unsigned)n_tokens), dim3(WARPS * 32),
+                              DECODE_SMEM_FUSED, (cudaStream_t)stream, (const bf16*)nullptr, (const bf16*)k_pages, (const bf16*)v_pages,
+                              scratch, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, fused);
     if (e != cudaSuccess) return (int)e;
     return (int)q3_launch(decode_capped_merge_kernel, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
                           (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink);

@@ -487,6 +487,31 @@ def attention_capped_decode(q, k_pages, v_pages, out, scratch, token_seq, token_
     return out
 
 
+def attention_capped_decode_fused(qkv, k_pages, v_pages, out, scratch, bias, cos, sin, token_seq, token_pos, page_table,
+                                  n_tokens: int, nq: int, nkv: int, d: int, vd: int, scale: float, softcap: float,
+                                  chunk: Optional[int], sink: bool, n_splits: int):
+    """`attention_capped_decode` from the output of the q/k/v projection as it is: the bias, the rotation of q and k and
+    the write of the new key and value into their pages happen in the attention's own kernel."""
+    if qkv.dtype != torch.bfloat16 or not attention_capped_fits(d, vd, None, nq // nkv):
+        raise KernelError("attention_capped_decode_fused: bfloat16, head sizes in steps of 16 up to 256, groups of up to 16 heads")
+    if qkv.shape[-1] != (nq + nkv) * d + nkv * vd or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) \
+            or v_pages.shape[1:] != (nkv, PAGE_TOKENS, vd) or out.shape[-1] != nq * vd \
+            or scratch.numel() < n_tokens * nq * n_splits * (vd + 2) or (bias is not None and bias.numel() != qkv.shape[-1]):
+        raise KernelError("attention_capped_decode_fused: shapes do not fit")
+    rot = _rotary_dim(cos, sin, d)
+    fn = _fn("attention_capped.cu", "q3_attention_capped_decode_fused_bf16",
+             [c_void_p] * 8 + [c_int] + [c_void_p] * 3 + [c_int, c_int64, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p],
+             defines=_capped_defines(d, vd))
+    _check(fn(_dev(qkv, "qkv"), _dev(k_pages, "k_pages", torch.bfloat16), _dev(v_pages, "v_pages", torch.bfloat16),
+              _dev(out, "out", torch.bfloat16), _dev(scratch, "scratch", torch.float32), _ptr(bias, "bias", torch.float32),
+              _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32), rot, _dev(token_seq, "token_seq", torch.int32),
+              _dev(token_pos, "token_pos", torch.int32), _dev(page_table, "page_table", torch.int32), page_table.shape[-1],
+              n_tokens, nq, nkv, float(scale), float(softcap or 0.0), int(chunk or 0), int(bool(sink)), int(n_splits), _stream()),
+           "attention_capped_decode_fused")
+    _count_extra(1)
+    return out
+
+
 def attention_capped_prefill_tc_fits(d: int, vd: int, window: Optional[int]) -> bool:
     return d in (64, 128) and vd == d and not window
 

@@ -95,6 +95,12 @@ int q3_attention_generic_bf16(const void* q, const void* k_pages, const void* v_
                               const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
                               float scale, int window, int value_dim, float softcap, int chunk, int sink, void* stream);
 
+/* the same from the q/k/v projection's output as it is: bias (may be null), rotation of the first rotary_dim values of q and k
+   (tables may be null) and the write of the new key and value into their pages in the attention's own kernel */
+int q3_attention_capped_decode_fused_bf16(const void* qkv, void* k_pages, void* v_pages, void* out, float* scratch, const float* bias,
+                                          const float* cos_tab, const float* sin_tab, int rotary_dim, const int* token_seq,
+                                          const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,
+                                          int nkv, float scale, float softcap, int chunk, int sink, int n_splits, void* stream);
 /* attention_prefill_tc.cu compiled with -DQ3_CAPPED=1: the tcgen05 prompt attention with capped scores, chunks and a sink
    (head sizes 64 and 128, values as wide as keys); arguments as q3_attention_prefill_tc_bf16 plus softcap, chunk, sink */
 int q3_attention_capped_prefill_tc_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* seq_start,

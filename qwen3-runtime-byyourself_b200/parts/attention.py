@@ -310,6 +310,20 @@ def _decode_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     return True
 
 
+def _decode_capped_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
+    """Bias, rotation, cache write and the split-key attention of a decode step in one kernel (and the small merge)."""
+    nq, nkv = part.num_heads, part.num_kv_heads
+    if part.plain or q_norm_w is not None or cache.shared \
+            or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
+        return False
+    splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device), part.chunk or ctx.max_context)
+    scratch = ctx.scratch.get("attn.capped_scratch", (ctx.n_tokens * nq * splits * (part.value_dim + 2),), torch.float32)
+    ops.attention_capped_decode_fused(qkv, cache.keys, cache.values, out, scratch, part.bias, cos, sin, ctx.token_seq,
+                                      ctx.token_pos, table, ctx.n_tokens, nq, nkv, part.head_dim, part.value_dim, part.scale,
+                                      part.softcap, part.chunk, part.sink, splits)
+    return True
+
+
 long_context_keys = 4096  # a decode step whose sequences may be longer takes wider clusters (if they are few)
 wide_cluster_blocks = 200 # blocks of a decode step with clusters beyond the portable size
 tc_prefill_rows = 128     # from this many new tokens of the longest sequence on, the tcgen05 kernel runs
@@ -320,6 +334,7 @@ fused_projection_rows = 2048
 
 DECODE_KERNELS.append(_decode_split_kernel)
 FUSED_DECODE_KERNELS.append(_decode_fused_kernel)
+FUSED_DECODE_KERNELS.append(_decode_capped_fused_kernel)
 FUSED_PROJECTION_KERNELS.append(_projection_pair_kernel)
 PREFILL_KERNELS.append(_prefill_tcgen05_kernel)
 PREFILL_KERNELS.append(_prefill_flash_kernel)

@@ -338,6 +338,47 @@ def test_tensor_core_attention_over_pages_at_every_edge(nq, nkv, d, vd, scale, c
     decode([(2, 0), (1, 130), (0, 64)], 5)
 
 
+@pytest.mark.parametrize("nq,nkv,d,vd,rot,chunk", [(8, 2, 64, 32, 32, 200), (4, 4, 16, 48, 16, 40), (6, 1, 128, 128, 64, 0)])
+def test_decode_attention_that_prepares_its_own_rows(nq, nkv, d, vd, rot, chunk):
+    """The decode attention in its fused form (bias, rotation and cache write inside) against the same step done by
+    qkv_prepare and the unfused kernel: the same outputs and the same cache, at positions on both sides of chunk and
+    page edges, first tokens included."""
+    import torch
+    from qwen3_b200.csrc import ops
+    from qwen3_b200.parts.position import RotaryEmbedding
+    rng = np.random.default_rng(d + vd)
+    part = RotaryEmbedding(d, 10000.0, 1024, rot)
+    part.prepare(512, "cuda")
+    lengths = [0, 1, 63, 64, 65, (chunk or 100) - 1, chunk or 100, (chunk or 100) + 1, 300, 191, 192]     # tokens cached before the step
+    n = len(lengths)
+    pages_per_seq = 5
+    n_pages = n * pages_per_seq + 1
+    table = torch.tensor(rng.permutation(n_pages - 1)[:n * pages_per_seq].reshape(n, pages_per_seq), dtype=torch.int32, device="cuda")
+    base_k = torch.tensor(rng.standard_normal((n_pages, nkv, 64, d)) * 0.5, dtype=torch.bfloat16, device="cuda")
+    base_v = torch.tensor(rng.standard_normal((n_pages, nkv, 64, vd)), dtype=torch.bfloat16, device="cuda")
+    width = (nq + nkv) * d + nkv * vd
+    qkv = torch.tensor(rng.standard_normal((n, width)), dtype=torch.bfloat16, device="cuda")
+    bias = torch.tensor(rng.standard_normal(width) * 0.5, dtype=torch.float32, device="cuda")
+    seq = torch.arange(n, dtype=torch.int32, device="cuda")
+    pos = torch.tensor(lengths, dtype=torch.int32, device="cuda")
+    # unfused: prepare, then attend
+    k1, v1 = base_k.clone(), base_v.clone()
+    q = torch.empty((n, nq * d), dtype=torch.bfloat16, device="cuda")
+    ops.qkv_prepare(qkv, q, k1, v1, None, None, part.cos, part.sin, seq, pos, table, n, nq, nkv, d, 0.0, bias=bias, value_dim=vd)
+    want = torch.empty((n, nq * vd), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(n * nq * 16 * (vd + 2), dtype=torch.float32, device="cuda")
+    ops.attention_capped_decode(q, k1, v1, want, scratch, seq, pos, table, n, nq, nkv, d, vd, 0.2, 9.0, chunk or None, True, 3)
+    for splits in (1, 3, 16):
+        k2, v2 = base_k.clone(), base_v.clone()
+        got = torch.full((n, nq * vd), 7.0, dtype=torch.bfloat16, device="cuda")
+        scratch.fill_(float("nan"))
+        ops.attention_capped_decode_fused(qkv, k2, v2, got, scratch, bias, part.cos, part.sin, seq, pos, table, n, nq, nkv, d, vd,
+                                          0.2, 9.0, chunk or None, True, splits)
+        assert torch.equal(k1, k2) and torch.equal(v1, v2), splits
+        err = float((got.float() - want.float()).abs().max())
+        assert err <= 2e-2, (splits, err)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_projection_rows_get_bias_rotation_and_their_place_in_the_pages(dtype):
     """qkv_prepare with a bias, values of another size than keys and a rotation over part of the head."""
