@@ -126,8 +126,8 @@ class DozazenConfig:
             vdim = _opt(m, "vdim", int, w) or dim
             if heads <= 0 or kv <= 0 or heads % kv:
                 raise ConfigError(f"{w}heads must be a positive multiple of kv_heads")
-            if dim <= 0 or dim % 2 or dim > 256 or vdim <= 0 or vdim > 256:
-                raise ConfigError(f"{w}dim {dim}, vdim {vdim}: this library runs even key sizes and any value size, up to 256")
+            if dim <= 0 or dim > 256 or vdim <= 0 or vdim > 256:
+                raise ConfigError(f"{w}dim {dim}, vdim {vdim}: this library runs head sizes up to 256")
             _get(m, "scale", float, w)
             cap = _opt(m, "softcap", float, w)
             if cap is not None and cap <= 0:

@@ -304,9 +304,10 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
                        const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps,
                        int write_kv, int rot, const float* bias, int vd, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0 || d % 2 != 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0) return Q3_ERR_BAD_SIZE;
+    if (d <= 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0) return Q3_ERR_BAD_SIZE;
     if (rot <= 0) rot = d;                       // the whole head is rotated
-    if (rot % 2 != 0 || rot > d) return Q3_ERR_BAD_SIZE;
+    if (rot > d || (rot % 2 != 0 && (cos_tab != nullptr || rot != d))) return Q3_ERR_BAD_SIZE;   // pairs need an even count
+    if (rot % 2 != 0) rot = 0;                   // an odd head without tables: every value passes through
     if (vd <= 0) vd = d;                         // values as wide as keys
     if (vd > MAX_HEAD_DIM) return Q3_ERR_BAD_SIZE;
     constexpr int VEC = Pack<T>::N;

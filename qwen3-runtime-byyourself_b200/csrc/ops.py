@@ -387,8 +387,8 @@ def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, toke
     value per column of the projection) is added first; `value_dim` is the size of a value head if not `d`."""
     s = _suffix(qkv)
     vd = int(value_dim or d)
-    if d % 2 != 0 or not 0 < d <= 256 or not 0 < vd <= 256:
-        raise KernelError(f"head_dim {d} / value_dim {vd} is not supported: even key sizes and any value size up to 256")
+    if not 0 < d <= 256 or not 0 < vd <= 256 or (d % 2 != 0 and cos is not None and 2 * cos.shape[-1] == d):
+        raise KernelError(f"head_dim {d} / value_dim {vd} is not supported: sizes up to 256, an even number of rotated values")
     if qkv.shape[-1] != (nq + nkv) * d + nkv * vd or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) \
             or v_pages.shape[1:] != (nkv, PAGE_TOKENS, vd) or (bias is not None and bias.numel() != qkv.shape[-1]):
         raise KernelError("qkv_prepare: shapes do not fit")

@@ -55,9 +55,9 @@ class GQAAttention(Part):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         value_dim = int(value_dim or head_dim)
-        if head_dim % 2 or not 0 < head_dim <= 256 or not 0 < value_dim <= 256:
-            raise ValueError(f"head_dim {head_dim} (values {value_dim}): the attention kernels take even key sizes and any "
-                             f"value size up to 256 (the tensor-core kernels: multiples of 16)")
+        if not 0 < head_dim <= 256 or not 0 < value_dim <= 256:
+            raise ValueError(f"head_dim {head_dim} (values {value_dim}): the attention kernels take sizes up to 256 "
+                             f"(the tensor-core kernels: multiples of 16)")
         if window and chunk:
             raise ValueError("attention takes a window or chunks, not both")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim

@@ -32,8 +32,8 @@ class RotaryEmbedding(Part):
         rotated, in pairs (i, i + rotary_dim/2) with inv_freq_i = theta^(-2i/rotary_dim); the rest pass through.
         `interleaved`: pairs (2i, 2i + 1) instead.  `scaling`: {factor, low, high, original}, see the top of the file."""
         rotary_dim = int(rotary_dim) or int(head_dim)
-        if head_dim % 2 or rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
-            raise ValueError("rotary encoding needs an even head_dim and an even rotary_dim within it")
+        if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
+            raise ValueError("rotary encoding needs an even rotary_dim within the head")
         self.head_dim, self.theta, self.max_positions = int(head_dim), float(theta), int(max_positions)
         self.rotary_dim = rotary_dim
         self.interleaved = bool(interleaved)

@@ -62,7 +62,18 @@ Z_C = {
          "mixer": _mixer(4, 1, 32, 64, 0.2, {"base": 100000.0, "dims": 32}, 25.0, 96)},
     ],
 }
-CASES = {"A": Z_A, "B": Z_B, "B1": Z_B1, "C": Z_C}
+# Sizes that rule out every vector path: a width that is no multiple of 4, odd head sizes and vocabulary, chunks of one
+# position (a token sees itself and the sink) and of seven.
+Z_D = {
+    "architecture": "Dozazen", "vocab": 97, "width": 50, "embedding": {"scale": 0.5}, "norm": {"eps": 1e-5},
+    "logit_scale": 3.0, "logit_softcap": 4.0, "loop": {"start": 1, "stop": 2, "times": 2},
+    "layers": [
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 30},
+         "mixer": _mixer(2, 1, 11, 7, 0.3, {"base": 50.0, "dims": 6}, 3.0, 7)},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 21}, "mixer": _mixer(5, 5, 6, 9, 0.4, {"base": 50.0, "dims": 6}, None, 1)},
+    ],
+}
+CASES = {"A": Z_A, "B": Z_B, "B1": Z_B1, "C": Z_C, "D": Z_D}
 
 
 def case(name, **changes):

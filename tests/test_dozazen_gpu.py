@@ -205,7 +205,8 @@ def attention_cases():
     # (query heads, kv heads, d, vd, scale, softcap, chunk, sink)
     return [(4, 2, 32, 16, 0.3, 8.0, 40, True), (6, 1, 24, 20, 0.25, 0.0, 96, True), (2, 2, 64, 64, 0.125, 30.0, 64, True),
             (8, 2, 64, 32, 0.2, 15.0, 200, True), (3, 3, 16, 48, 0.5, 5.0, 0, True), (4, 1, 128, 128, 0.09, 20.0, 128, False),
-            (4, 2, 128, 128, 0.09, 25.0, 100, True), (2, 1, 64, 64, 0.125, 0.0, 0, True), (2, 2, 64, 64, 0.125, 10.0, 72, False)]
+            (4, 2, 128, 128, 0.09, 25.0, 100, True), (2, 1, 64, 64, 0.125, 0.0, 0, True), (2, 2, 64, 64, 0.125, 10.0, 72, False),
+            (2, 1, 64, 64, 0.125, 5.0, 1, True), (3, 1, 11, 7, 0.3, 3.0, 7, True)]
 
 
 def edge_positions(n, chunk):
@@ -425,7 +426,7 @@ def test_projection_rows_get_bias_rotation_and_their_place_in_the_pages(dtype):
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     base = tmp_path_factory.mktemp("dozazen")
-    return {name: make_folder(base, case(name), seed=17 + i, name=name) for i, name in enumerate(["A", "B", "B1", "C"])}
+    return {name: make_folder(base, case(name), seed=17 + i, name=name) for i, name in enumerate(["A", "B", "B1", "C", "D"])}
 
 
 def engine_for(folder, dtype, max_tokens, **kw):
@@ -464,7 +465,7 @@ def check(got, requests, name, weights, dtype, label):
             assert err <= tol, f"{label} [{dtype}] case {name}: request {rid} position {p} of {len(toks)}: {err:.3e} > {tol:.3e}"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "B1", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "B1", "C", "D"])
 def test_hidden_state_after_every_layer_run(folders, name):
     """32-bit: the stream after each run of a layer (a repeated layer counts each time) against the plain model."""
     import torch
@@ -494,7 +495,7 @@ def test_hidden_state_after_every_layer_run(folders, name):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,lengths", [("A", [1, 2, 39, 40, 41, 141, 300]), ("B", [63, 64, 65, 129, 260]),
-                                          ("B1", [5, 200]), ("C", [96, 97, 201, 450])])
+                                          ("B1", [5, 200]), ("C", [96, 97, 201, 450]), ("D", [1, 8, 70, 150])])
 def test_whole_requests(folders, name, lengths, dtype):
     folder, weights = folders[name]
     requests = make_requests(case(name), lengths, seed=1)
@@ -507,7 +508,7 @@ def test_whole_requests(folders, name, lengths, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name,lengths,tail", [("A", [30, 100, 215], 90), ("B", [70, 200], 70), ("C", [230, 420], 100)])
+@pytest.mark.parametrize("name,lengths,tail", [("A", [30, 100, 215], 90), ("B", [70, 200], 70), ("C", [230, 420], 100), ("D", [20, 90], 40)])
 def test_prompt_then_token_by_token_across_chunk_edges(folders, name, lengths, tail, dtype):
     """The last `tail` tokens one a step: decoding passes over chunk and page edges (a request shorter than the
     tail goes token by token from its first token)."""
@@ -623,3 +624,18 @@ def test_trace_replay_from_the_command_line(tmp_path, folders, dtype):
             exact, bf16_tol = oracle("A", weights, requests[rid])
             err = float(np.max(np.abs(got[(tag, p)] - exact[p])))
             assert err <= (FP32_TOL if dtype == "float32" else bf16_tol), (tag, p, err)
+
+
+def test_the_command_line_generates_from_token_ids(folders):
+    """bin/qwen3_chat on a Dozazen folder: the model class comes from config.json, the design has no stop tokens of its own."""
+    folder, weights = folders["A"]
+    cfg = case("A")
+    prompts = [[7, 8, 9], [100, 3]]
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qwen3_chat"), folder, "--greedy", "--dtype", "float32",
+                          "--max-new-tokens", "6", "--max-context", "64", "--tokens", "7,8,9", "--tokens", "100 3"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.strip().splitlines() if l and l[0].isdigit()]
+    assert len(lines) == 2
+    for p, line in zip(prompts, lines):
+        assert [int(t) for t in line.split("#")[0].strip().split(",")] == plain.generate_greedy(cfg, weights, p, 6)

@@ -205,9 +205,9 @@ def test_8b_widths_in_unequal_batches(wide, dtype, monkeypatch):
         calls["pair_qkv"] += 1
         return real_qkv(*a, **k)
 
-    def pair(x, w, out, gated=False, splits=1):
+    def pair(x, w, out, gated=False, splits=1, **k):
         calls["pair_gated" if gated else "pair"] += 1
-        return real_pair(x, w, out, gated, splits)
+        return real_pair(x, w, out, gated, splits, **k)
 
     def tc(*a, **k):
         calls["attention_tc"] += 1
