@@ -349,10 +349,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     float t0, t1, t2, t3;
                     unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), tanh_k2), t0, t1);
                     unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), tanh_k2), t2, t3);
+                    // beyond 2^60 the tanh is 1 to the last bit; the bound keeps the products below finite
+                    t0 = fminf(t0, 60.0f); t1 = fminf(t1, 60.0f); t2 = fminf(t2, 60.0f); t3 = fminf(t3, 60.0f);
                     unpack_f32x2(add_f32x2(pack_f32x2(ex2_approx(t0), ex2_approx(t1)), one2), t0, t1);
                     unpack_f32x2(add_f32x2(pack_f32x2(ex2_approx(t2), ex2_approx(t3)), one2), t2, t3);
-                    unpack_f32x2(fma_f32x2(pack_f32x2(rcp_approx(t0), rcp_approx(t1)), slope2, shift2), x0, x1);
-                    unpack_f32x2(fma_f32x2(pack_f32x2(rcp_approx(t2), rcp_approx(t3)), slope2, shift2), x2, x3);
+                    // the special-function unit is what bounds this loop: one reciprocal serves two scores,
+                    // 1/a = b / (a b) and 1/b = a / (a b)
+                    const float r01 = rcp_approx(t0 * t1), r23 = rcp_approx(t2 * t3);
+                    unpack_f32x2(fma_f32x2(mul_f32x2(pack_f32x2(t1, t0), pack_f32x2(r01, r01)), slope2, shift2), x0, x1);
+                    unpack_f32x2(fma_f32x2(mul_f32x2(pack_f32x2(t3, t2), pack_f32x2(r23, r23)), slope2, shift2), x2, x3);
                     if (edge) {                          // a key that is not seen has a capped score too: take it out again
                         if (s[c] == 0xff800000u) x0 = -INFINITY;
                         if (s[c + 1] == 0xff800000u) x1 = -INFINITY;
