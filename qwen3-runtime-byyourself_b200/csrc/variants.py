@@ -15,4 +15,7 @@ def all_variants():
         ("attention_decode_static.cu", ("Q3_HEAD_DIM=128",)),
         ("gemm_tcgen05.cu", ()),
         ("attention_prefill_tc.cu", ("Q3_HEAD_DIM=128",)),
+        ("stream_f32.cu", ()),
+        ("attention_capped.cu", ("Q3_HEAD_DIM=128", "Q3_VALUE_DIM=128")),
+        ("attention_prefill_tc.cu", ("Q3_HEAD_DIM=128", "Q3_CAPPED=1")),
     ]

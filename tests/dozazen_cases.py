@@ -53,13 +53,13 @@ Z_B1 = dict(copy.deepcopy(Z_B), loop={"start": 0, "stop": 1, "times": 1})
 # Sizes that the tensor-core kernels take (head sizes in steps of 16, widths in steps of 8), every layer twice.
 Z_C = {
     "architecture": "Dozazen", "vocab": 320, "width": 128, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-5},
-    "logit_scale": 2.5, "logit_softcap": 20.0, "loop": {"start": 0, "stop": 2, "times": 2},
+    "logit_scale": 2.5, "logit_softcap": 11.0, "loop": {"start": 0, "stop": 2, "times": 2},
     "layers": [
         {"type": "attention", "mlp": {"kind": "dense", "ff": 256},
          "mixer": _mixer(8, 2, 64, 32, 0.125, {"base": 100000.0, "dims": 32,
-                                               "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 256}}, 15.0, 200)},
+                                               "scaling": {"factor": 6.0, "low": 1.5, "high": 5.0, "original": 256}}, 17.0, 200)},
         {"type": "attention", "mlp": {"kind": "dense", "ff": 256},
-         "mixer": _mixer(4, 1, 32, 64, 0.2, {"base": 100000.0, "dims": 32}, 25.0, 96)},
+         "mixer": _mixer(4, 1, 32, 64, 0.2, {"base": 100000.0, "dims": 32}, 25.0, 104)},
     ],
 }
 # Sizes that rule out every vector path: a width that is no multiple of 4, odd head sizes and vocabulary, chunks of one

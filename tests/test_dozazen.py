@@ -121,7 +121,7 @@ def test_interleaved_rotation_equals_the_half_split_one_on_reordered_values():
 
 def test_chunk_groups_return_the_pages_of_finished_chunks():
     from qwen3_b200.cache import CacheBook, CacheNeed
-    book = CacheBook([CacheNeed("chunk", 1, 16, window=96), CacheNeed("full", 1, 16), CacheNeed("chunk", 2, 16, window=64, value_dim=8)],
+    book = CacheBook([CacheNeed("chunk", 1, 16, window=80), CacheNeed("full", 1, 16), CacheNeed("chunk", 2, 16, window=64, value_dim=8)],
                      max_tokens=64 * 12, max_seq_len=64 * 8)
     assert len(book.groups) == 3
     s = book.alloc_slot()
@@ -133,14 +133,14 @@ def test_chunk_groups_return_the_pages_of_finished_chunks():
         book.reserve([(s, n)])
         book.commit([(s, n)])
 
-    step(95)                    # positions 0..94: the first chunk of 96 is still open
+    step(79)                    # positions 0..78: the first chunk of 80 is still open
     assert (held(0), held(1), held(2)) == (2, 2, 1)          # the chunks of 64: page 0 is finished
-    step(1)                     # length 96: the next query opens chunk [96, 192), which starts inside page 1
+    step(1)                     # length 80: the next query opens chunk [80, 160), which starts inside page 1
     assert (held(0), held(1), held(2)) == (1, 2, 1)
-    step(97)                    # length 193: chunk [192, 288) starts at page 3 exactly
-    assert (held(0), held(1), held(2)) == (1, 4, 1)
-    step(200)                   # length 393: chunk [384, 480) starts at page 6; a portion that crossed chunks held all its pages
-    assert (held(0), held(1), held(2)) == (1, 7, 1)
+    step(81)                    # length 161: chunk [160, 240) starts inside page 2
+    assert (held(0), held(1), held(2)) == (1, 3, 1)
+    step(200)                   # length 361: chunk [320, 400) starts at page 5; a portion that crossed chunks held all its pages
+    assert (held(0), held(1), held(2)) == (1, 6, 1)
     other = book.alloc_slot()
     book.reserve([(other, 130)])                               # pages given back are handed out again
     book.commit([(other, 130)])

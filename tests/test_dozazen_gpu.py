@@ -203,7 +203,7 @@ class Paged:
 
 def attention_cases():
     # (query heads, kv heads, d, vd, scale, softcap, chunk, sink)
-    return [(4, 2, 32, 16, 0.3, 8.0, 40, True), (6, 1, 24, 20, 0.25, 0.0, 96, True), (2, 2, 64, 64, 0.125, 30.0, 64, True),
+    return [(4, 2, 32, 16, 0.3, 8.0, 40, True), (6, 1, 24, 20, 0.25, 0.0, 90, True), (2, 2, 64, 64, 0.125, 30.0, 64, True),
             (8, 2, 64, 32, 0.2, 15.0, 200, True), (3, 3, 16, 48, 0.5, 5.0, 0, True), (4, 1, 128, 128, 0.09, 20.0, 128, False),
             (4, 2, 128, 128, 0.09, 25.0, 100, True), (2, 1, 64, 64, 0.125, 0.0, 0, True), (2, 2, 64, 64, 0.125, 10.0, 72, False),
             (2, 1, 64, 64, 0.125, 5.0, 1, True), (3, 1, 11, 7, 0.3, 3.0, 7, True)]
@@ -495,7 +495,7 @@ def test_hidden_state_after_every_layer_run(folders, name):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,lengths", [("A", [1, 2, 39, 40, 41, 141, 300]), ("B", [63, 64, 65, 129, 260]),
-                                          ("B1", [5, 200]), ("C", [96, 97, 201, 450]), ("D", [1, 8, 70, 150])])
+                                          ("B1", [5, 200]), ("C", [104, 105, 201, 450]), ("D", [1, 8, 70, 150])])
 def test_whole_requests(folders, name, lengths, dtype):
     folder, weights = folders[name]
     requests = make_requests(case(name), lengths, seed=1)
@@ -523,7 +523,7 @@ def test_prompt_then_token_by_token_across_chunk_edges(folders, name, lengths, t
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name,length,cuts", [
     ("A", 260, [2, 4, 39, 41, 80, 82, 120, 190, 258]), ("A", 150, list(range(2, 150, 2))),
-    ("B", 200, [63, 65, 128, 130]), ("C", 420, [95, 97, 199, 201, 203, 400])])
+    ("B", 200, [63, 65, 128, 130]), ("C", 420, [103, 105, 199, 201, 203, 400])])
 def test_prompts_fed_in_portions(folders, name, length, cuts, dtype):
     """Portions of many sizes, down to two tokens, that start and end at, before and after chunk and page edges."""
     folder, weights = folders[name]
@@ -539,7 +539,7 @@ def test_prompts_fed_in_portions(folders, name, length, cuts, dtype):
 @pytest.mark.parametrize("name,lengths,prompts,batch", [
     ("A", [13, 130, 9, 90, 66, 45, 128, 3], [5, 100, 1, 64, 65, 40, 39, 3], 3),
     ("B", [140, 70, 200, 66], [130, 1, 64, 63], 2),
-    ("C", [300, 110, 9, 260, 210], [199, 96, 1, 201, 95], 3),
+    ("C", [300, 110, 9, 260, 210], [199, 104, 1, 201, 103], 3),
 ])
 def test_unequal_batches_one_after_another(folders, name, lengths, prompts, batch, dtype):
     """Requests of different lengths start together and are decoded together; the shorter ones end earlier; the
