@@ -159,6 +159,23 @@ int sandwich_norm_launch(float* stream, const T* branch, const float* w_post, co
 }
 
 // ---------------------------------------------------------------- [a; b] in the compute type
+// Four values a thread where the rows allow 16-byte reads.
+template <typename T>
+__global__ void concat_cast_vec_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int64_t rows,
+                                       int size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int groups = size / 4;
+    const int64_t total = rows * 2 * groups;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / (2 * groups);
+        const int g = (int)(i % (2 * groups));
+        float v[4];
+        load4<float>((g < groups ? a + r * size : b + r * size - size) + 4 * g, v);
+        store4<T>(out + r * 2 * size + 4 * g, v);
+    }
+}
+
 template <typename T>
 __global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int64_t rows,
                                    int size) {
@@ -222,6 +239,9 @@ static unsigned grid_for(int64_t work, int threads) {
     Q3_EXPORT int q3_concat_cast_##SUFFIX(const float* a, const float* b, void* out, int64_t rows, int size, void* stream) { \
         if (rows <= 0) return 0;                                                                                         \
         if (size <= 0) return Q3_ERR_BAD_SIZE;                                                                           \
+        if (size % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(out))                                             \
+            return (int)q3_launch(concat_cast_vec_kernel<T>, dim3(grid_for(rows * 2 * (size / 4), 256)), dim3(256), 0,   \
+                                  (cudaStream_t)stream, a, b, (T*)out, rows, size);                                      \
         return (int)q3_launch(concat_cast_kernel<T>, dim3(grid_for(rows * 2 * size, 256)), dim3(256), 0,                 \
                               (cudaStream_t)stream, a, b, (T*)out, rows, size);                                          \
     }                                                                                                                    \

@@ -50,6 +50,7 @@ Z_B = {
     ],
 }
 Z_B1 = dict(copy.deepcopy(Z_B), loop={"start": 0, "stop": 1, "times": 1})
+Z_B1["layers"][1]["mixer"].update(heads=34, kv_heads=1)      # more query heads per key/value head than a tensor-core tile has rows
 # Sizes that the tensor-core kernels take (head sizes in steps of 16, widths in steps of 8), every layer twice.
 Z_C = {
     "architecture": "Dozazen", "vocab": 320, "width": 128, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-5},

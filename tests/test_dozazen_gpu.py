@@ -206,7 +206,8 @@ def attention_cases():
     return [(4, 2, 32, 16, 0.3, 8.0, 40, True), (6, 1, 24, 20, 0.25, 0.0, 90, True), (2, 2, 64, 64, 0.125, 30.0, 64, True),
             (8, 2, 64, 32, 0.2, 15.0, 200, True), (3, 3, 16, 48, 0.5, 5.0, 0, True), (4, 1, 128, 128, 0.09, 20.0, 128, False),
             (4, 2, 128, 128, 0.09, 25.0, 100, True), (2, 1, 64, 64, 0.125, 0.0, 0, True), (2, 2, 64, 64, 0.125, 10.0, 72, False),
-            (2, 1, 64, 64, 0.125, 5.0, 1, True), (3, 1, 11, 7, 0.3, 3.0, 7, True)]
+            (2, 1, 64, 64, 0.125, 5.0, 1, True), (3, 1, 11, 7, 0.3, 3.0, 7, True), (5, 5, 80, 48, 0.11, 12.0, 50, True),
+            (12, 1, 32, 32, 0.18, 7.0, 130, True)]
 
 
 def edge_positions(n, chunk):
@@ -606,8 +607,11 @@ def test_greedy_generation_through_the_entry_point(folders, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_trace_replay_from_the_command_line(tmp_path, folders, dtype):
+def test_trace_replay_from_the_command_line(tmp_path, folders, dtype, monkeypatch):
     from test_trace_run_gpu import replay
+    # --max-tokens counts the tokens of the live requests without the padding of their last pages
+    unpadded = schedules.peak_tokens
+    monkeypatch.setattr(schedules, "peak_tokens", lambda steps, page=64: unpadded(steps, 1))
     folder, weights = folders["A"]
     cfg = case("A")
     requests = make_requests(cfg, [75, 1, 130], seed=8)
