@@ -25,8 +25,9 @@
 //   s <- cap * tanh(dot * scale / cap) (cap 0: dot * scale), with tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1) on the
 //   special-function unit; a query sees the keys of its own chunk of `chunk` positions only (0: all before it),
 //   so a tile's pages start at the page of its first row's chunk start; with a sink the running maximum
-//   starts at 0 and the running sum at the sink's weight.  The softmax and its weights are computed in 32-bit;
-//   the weights enter the second product rounded to bfloat16, as the operands of every product are.
+//   starts at 0 and the running sum at the sink's weight.  The softmax and its weights are computed in 32-bit and
+//   enter the second product as two bfloat16 terms, p = hi + lo with hi = bf16(p) and lo = bf16(p - hi) (TMEM
+//   columns [64,96) and [96,128), two sets of tcgen05.mma per page), so the product sees them to 16 bits of mantissa.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -64,7 +65,7 @@ constexpr int PANEL_BYTES = HALVES * PAGE * 128;         // one page of K (or V)
 // a kernel without static shared memory starts at a 1024-byte boundary (checked when the kernel starts)
 constexpr int SMEM_BYTES = Q_BYTES + (K_STAGES + V_STAGES) * PANEL_BYTES + 256;
 constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t COL_S = 0, COL_P = 64, COL_O = 128;
+constexpr uint32_t COL_S = 0, COL_P = 64, COL_P_LO = 96, COL_O = 128;   // COL_P_LO: the capped form's second term of the weights
 constexpr float RESCALE_THRESHOLD = 8.0f;                // in log2 units: probabilities stay below 2^8
 
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
@@ -267,6 +268,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 for (int kk = 0; kk < PAGE / 16; ++kk)
                     tc_mma_ts(tmem + COL_O, tmem + COL_P + kk * 8, desc_mn_major(v_src + kk * 16 * 128, PAGE * 128), idesc_pv,
                               (j > 0 || kk > 0) ? 1u : 0u);
+                if constexpr (CAPPED) {                                      // the low term of the weights on the same V
+#pragma unroll
+                    for (int kk = 0; kk < PAGE / 16; ++kk)
+                        tc_mma_ts(tmem + COL_O, tmem + COL_P_LO + kk * 8, desc_mn_major(v_src + kk * 16 * 128, PAGE * 128), idesc_pv, 1u);
+                }
                 tc_commit(bar_v_empty + 8 * (j % V_STAGES));                 // the page's V is consumed
                 tc_commit(bar_pv_done);
             }
@@ -338,6 +344,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(neg_m, neg_m);
             uint64_t part2[2] = {pack_f32x2(0.0f, 0.0f), pack_f32x2(0.0f, 0.0f)};
             uint32_t p[32];
+            uint32_t p_lo[CAPPED ? 32 : 1];
             // the capped form: x = cap_l2 * (1 - 2 / (2^(dot * tanh_k) + 1)) - m = -2 cap_l2 / (...) + (cap_l2 - m)
             const uint64_t tanh_k2 = pack_f32x2(tanh_k, tanh_k), one2 = pack_f32x2(1.0f, 1.0f);
             const uint64_t slope2 = pack_f32x2(-2.0f * cap_l2, -2.0f * cap_l2), shift2 = pack_f32x2(cap_l2 + neg_m, cap_l2 + neg_m);
@@ -353,8 +360,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     t0 = fminf(t0, 60.0f); t1 = fminf(t1, 60.0f); t2 = fminf(t2, 60.0f); t3 = fminf(t3, 60.0f);
                     unpack_f32x2(add_f32x2(pack_f32x2(ex2_approx(t0), ex2_approx(t1)), one2), t0, t1);
                     unpack_f32x2(add_f32x2(pack_f32x2(ex2_approx(t2), ex2_approx(t3)), one2), t2, t3);
-                    // the special-function unit is what bounds this loop: one reciprocal serves two scores,
-                    // 1/a = b / (a b) and 1/b = a / (a b)
+                    // one reciprocal serves two scores: 1/a = b / (a b) and 1/b = a / (a b)
                     const float r01 = rcp_approx(t0 * t1), r23 = rcp_approx(t2 * t3);
                     unpack_f32x2(fma_f32x2(mul_f32x2(pack_f32x2(t1, t0), pack_f32x2(r01, r01)), slope2, shift2), x0, x1);
                     unpack_f32x2(fma_f32x2(mul_f32x2(pack_f32x2(t3, t2), pack_f32x2(r23, r23)), slope2, shift2), x2, x3);
@@ -373,6 +379,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 part2[1] = add_f32x2(part2[1], pack_f32x2(e, f));
                 p[c >> 1] = pack_bf16(a, b);
                 p[(c >> 1) + 1] = pack_bf16(e, f);
+                if constexpr (CAPPED) {                  // what the rounding dropped, as a second bfloat16 term
+                    const uint32_t h0 = p[c >> 1], h1 = p[(c >> 1) + 1];
+                    p_lo[c >> 1] = pack_bf16(a - __uint_as_float(h0 << 16), b - __uint_as_float(h0 & 0xffff0000u));
+                    p_lo[(c >> 1) + 1] = pack_bf16(e - __uint_as_float(h1 << 16), f - __uint_as_float(h1 & 0xffff0000u));
+                }
             }
             float part[4];
             unpack_f32x2(part2[0], part[0], part[1]);
@@ -402,6 +413,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
             }
             tc_st32(t_row + COL_P, p);
+            if constexpr (CAPPED) tc_st32(t_row + COL_P_LO, p_lo);
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
