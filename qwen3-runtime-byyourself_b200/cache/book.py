@@ -33,7 +33,9 @@ class CacheNeed:
     `window` tokens; 'chunk': of the tokens in the query's own chunk of `window`
     positions (chunks counted from position 0); 'none': no keys.  `state_shape` is
     a fixed-size float32 area per sequence (empty: none); it can go with any kind.
-    `value_dim` is the size of a value row where it differs from the key's `head_dim`.
+    `value_dim` is the size of a value row where it differs from the key's `head_dim`;
+    `value_heads` the number of value heads where it differs from `num_kv_heads` (values
+    that several key heads share).
     """
     kind: str = "none"
     num_kv_heads: int = 0
@@ -41,6 +43,7 @@ class CacheNeed:
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     value_dim: Optional[int] = None
+    value_heads: Optional[int] = None
 
     def __post_init__(self):
         if self.kind not in ("full", "window", "chunk", "none"):
@@ -52,7 +55,7 @@ class CacheNeed:
 
     def group_key(self):
         return (self.kind, self.num_kv_heads, self.head_dim, self.window if self.kind in ("window", "chunk") else None,
-                self.value_dim or self.head_dim)
+                self.value_dim or self.head_dim, self.value_heads or self.num_kv_heads)
 
 
 class CacheError(RuntimeError):

@@ -40,12 +40,13 @@ class KVCache(CacheBook):
         self.stores = []          # per group: one tensor [layer, K|V, ...], or a (keys, values) pair of [layer, ...]
         for g in self.groups:
             shape = (g.n_pages + 1, g.need.num_kv_heads, PAGE_TOKENS)
-            vd = g.need.value_dim or g.need.head_dim
-            if vd == g.need.head_dim:
+            vd, nv = g.need.value_dim or g.need.head_dim, g.need.value_heads or g.need.num_kv_heads
+            if vd == g.need.head_dim and nv == g.need.num_kv_heads:
                 self.stores.append(torch.zeros((len(g.layers), 2) + shape + (vd,), dtype=dtype, device=self.device))
             else:
                 self.stores.append((torch.zeros((len(g.layers),) + shape + (g.need.head_dim,), dtype=dtype, device=self.device),
-                                    torch.zeros((len(g.layers),) + shape + (vd,), dtype=dtype, device=self.device)))
+                                    torch.zeros((len(g.layers), g.n_pages + 1, nv, PAGE_TOKENS, vd), dtype=dtype,
+                                                device=self.device)))
         self.states = {layer: torch.zeros((self.n_slots + 1,) + shape, dtype=torch.float32, device=self.device)
                        for layer, shape in self.state_layers.items()}
         self._views: Dict[int, LayerCache] = {}
@@ -72,5 +73,6 @@ class KVCache(CacheBook):
 
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.layers) * g.need.num_kv_heads * (g.need.head_dim + (g.need.value_dim or g.need.head_dim)) * item
+        return sum(len(g.layers) * (g.need.num_kv_heads * g.need.head_dim
+                                    + (g.need.value_heads or g.need.num_kv_heads) * (g.need.value_dim or g.need.head_dim)) * item
                    for g in self.groups)

@@ -4,6 +4,7 @@ from .registry import (ConfigError, config_class_for, config_from_dict, known_ar
                        load_config, register_architecture)
 from .qwen3 import Qwen3Config
 from .dozazen import DozazenConfig
+from .lagulorn import LagulornConfig
 
 __all__ = ["LayerSpec", "ModelPlan", "PartSpec", "StreamStep", "ConfigError", "config_class_for", "config_from_dict",
-           "known_architectures", "load_config", "register_architecture", "Qwen3Config", "DozazenConfig"]
+           "known_architectures", "load_config", "register_architecture", "Qwen3Config", "DozazenConfig", "LagulornConfig"]

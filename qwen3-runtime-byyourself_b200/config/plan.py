@@ -52,7 +52,9 @@ class ModelPlan:
     of layers are the layers' own caches, numbers from there on are further ones of the same kind
     as the layer's that uses them.  None: every run of a layer uses the layer's own cache.
     `stream_steps` run between layers; `residual_dtype` "float32" keeps the hidden state between
-    the parts in 32-bit whatever the compute type (None: in the compute type).
+    the parts in 32-bit whatever the compute type (None: in the compute type).  With `streams` > 1 the
+    hidden state is that many rows per token (the embedding fills them alike, the blocks mix them, and
+    the last block's `finish` sums them).
     """
     architecture: str
     vocab_size: int
@@ -71,6 +73,7 @@ class ModelPlan:
     stream_steps: List[StreamStep] = field(default_factory=list)
     residual_dtype: Optional[str] = None
     final_norm_name: Optional[str] = None     # the final norm's tensor (None: final_norm_prefix + "weight")
+    streams: int = 1                          # copies of the hidden state that travel side by side ([tokens, streams, hidden])
 
     def cache_of_run(self, run: int) -> int:
         return self.order[run] if self.caches is None else self.caches[run]
@@ -95,6 +98,8 @@ class ModelPlan:
         for step in self.stream_steps:
             if not 0 <= step.before_run < len(self.order):
                 raise ValueError(f"a stream step before run {step.before_run}, but the plan has {len(self.order)} runs")
+        if self.streams < 1 or (self.streams > 1 and self.residual_dtype != "float32"):
+            raise ValueError("streams is at least 1; several streams are kept in float32")
         if self.residual_dtype not in (None, "float32"):
             raise ValueError("residual_dtype is None (the compute type) or 'float32'")
         for i in self.order:

@@ -48,16 +48,16 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
                                    const float* __restrict__ sin_tab, const int* __restrict__ token_seq,
                                    const int* __restrict__ token_pos, const int* __restrict__ page_table,
                                    int pages_per_seq, int nq, int nkv, int d, float eps, int write_kv, int rot,
-                                   const float* __restrict__ bias, int vd) {
+                                   const float* __restrict__ bias, int vd, int nv) {
     pdl_launch_dependents();
     pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x * warps + warp;
-    if (head >= nq + 2 * nkv || (head >= nq && !write_kv)) return;   // a layer that reads another layer's cache writes none
+    if (head >= nq + nkv + nv || (head >= nq && !write_kv)) return;   // a layer that reads another layer's cache writes none
     const int64_t t = blockIdx.y;
     const int pos = token_pos[t];
-    // a row of the projection: nq query heads and nkv key heads of d values, then nkv value heads of vd values
-    const int64_t row = (int64_t)(nq + nkv) * d + (int64_t)nkv * vd;
+    // a row of the projection: nq query heads and nkv key heads of d values, then nv value heads of vd values
+    const int64_t row = (int64_t)(nq + nkv) * d + (int64_t)nv * vd;
     const int64_t col0 = head < nq + nkv ? (int64_t)head * d : (int64_t)(nq + nkv) * d + (int64_t)(head - nq - nkv) * vd;
     const T* src = qkv + t * row + col0;
     if (bias != nullptr) bias += col0;
@@ -69,10 +69,10 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_
         dst = q_out + t * (int64_t)nq * d + (int64_t)head * d;
         norm_w = q_norm_w;
     } else {
-        const int kvh = (head - nq) % nkv;
         const bool is_v = head >= nq + nkv;
+        const int kvh = is_v ? head - nq - nkv : head - nq;
         const int page = page_table[(int64_t)token_seq[t] * pages_per_seq + pos / PAGE];
-        dst = (is_v ? v_pages : k_pages) + (((int64_t)page * nkv + kvh) * PAGE + pos % PAGE) * (is_v ? vd : d);
+        dst = (is_v ? v_pages : k_pages) + (((int64_t)page * (is_v ? nv : nkv) + kvh) * PAGE + pos % PAGE) * (is_v ? vd : d);
         norm_w = is_v ? nullptr : k_norm_w;
         rotate = rotate && !is_v;
         if (is_v) {                                     // a value head: vd values that pass through
@@ -241,13 +241,13 @@ __global__ void __launch_bounds__(128)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                          T* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                          const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, int d, float scale,
-                         int window, int vd, float softcap, int chunk, int sink) {
+                         int window, int vd, float softcap, int chunk, int sink, int nv, int out_f32) {
     __shared__ float q_s[MAX_HEAD_DIM];
     __shared__ float score[PAGE];
     __shared__ float prob[PAGE];
     pdl_launch_dependents();
     pdl_wait();
-    const int head = blockIdx.x, kvh = head / (nq / nkv);
+    const int head = blockIdx.x, kvh = head / (nq / nkv), vh = kvh / (nkv / nv);   // nv value heads: each serves nkv / nv key heads
     const int64_t t = blockIdx.y;
     const int pos = token_pos[t];
     const int* pages = page_table + (int64_t)token_seq[t] * pages_per_seq;
@@ -261,9 +261,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     float m_run = sink ? 0.0f : -INFINITY, l_run = sink ? 1.0f : 0.0f, acc0 = 0.0f, acc1 = 0.0f;
     const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
     for (int pg = lo / PAGE; pg <= pos / PAGE; ++pg) {
-        const int64_t tile = ((int64_t)pages[pg] * nkv + kvh) * PAGE;
-        const T* kp = k_pages + tile * d;
-        const T* vp = v_pages + tile * vd;
+        const T* kp = k_pages + ((int64_t)pages[pg] * nkv + kvh) * PAGE * d;
+        const T* vp = v_pages + ((int64_t)pages[pg] * nv + vh) * PAGE * vd;
         const int j_lo = max(lo - pg * PAGE, 0), j_hi = min(pos - pg * PAGE, PAGE - 1);  // inclusive, in-page
         for (int j = warp; j < PAGE; j += 4) {
             float dot = 0.0f;
@@ -293,6 +292,12 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
         m_run = m_new;
         __syncthreads();  // score/prob are rewritten by the next page
     }
+    if (out_f32) {                                   // the caller goes on in 32-bit (differences of attention maps)
+        float* o = reinterpret_cast<float*>(out) + (t * nq + head) * (int64_t)vd;
+        if (tid < vd) o[tid] = acc0 / l_run;
+        if (tid + 128 < vd) o[tid + 128] = acc1 / l_run;
+        return;
+    }
     T* o = out + (t * nq + head) * (int64_t)vd;
     if (tid < vd) o[tid] = from_f32<T>(acc0 / l_run);
     if (tid + 128 < vd) o[tid + 128] = from_f32<T>(acc1 / l_run);
@@ -302,16 +307,17 @@ template <typename T>
 int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const float* q_norm_w, const float* k_norm_w,
                        const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos,
                        const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps,
-                       int write_kv, int rot, const float* bias, int vd, cudaStream_t stream) {
+                       int write_kv, int rot, const float* bias, int vd, int nv, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0) return Q3_ERR_BAD_SIZE;
+    if (nv <= 0) nv = nkv;                       // as many value heads as key heads
+    if (d <= 0 || d > MAX_HEAD_DIM || nq <= 0 || nkv <= 0 || nkv % nv != 0) return Q3_ERR_BAD_SIZE;
     if (rot <= 0) rot = d;                       // the whole head is rotated
     if (rot > d || (rot % 2 != 0 && (cos_tab != nullptr || rot != d))) return Q3_ERR_BAD_SIZE;   // pairs need an even count
     if (rot % 2 != 0) rot = 0;                   // an odd head without tables: every value passes through
     if (vd <= 0) vd = d;                         // values as wide as keys
     if (vd > MAX_HEAD_DIM) return Q3_ERR_BAD_SIZE;
     constexpr int VEC = Pack<T>::N;
-    if (rot == d && vd == d && n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
+    if (rot == d && vd == d && nv == nkv && n_tokens >= 64 && (d / 2) % VEC == 0 && (d / 2) / VEC <= 32 && aligned16(qkv) && aligned16(q_out) &&
         aligned16(k_pages) && aligned16(v_pages)) {
         const int hpw = 32 / ((d / 2) / VEC);
         const int64_t n_warps = (n_tokens * (nq + 2 * nkv) + hpw - 1) / hpw;
@@ -323,25 +329,27 @@ int qkv_prepare_launch(const T* qkv, T* q_out, T* k_pages, T* v_pages, const flo
     }
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const int warps = 4;
-    const dim3 grid((nq + 2 * nkv + warps - 1) / warps, (unsigned)n_tokens);
+    const dim3 grid((nq + nkv + nv + warps - 1) / warps, (unsigned)n_tokens);
     return (int)q3_launch(qkv_prepare_kernel<T>, grid, dim3(warps * 32), 0, stream, qkv, q_out, k_pages, v_pages, q_norm_w,
                           k_norm_w, cos_tab, sin_tab, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, d, eps, write_kv, rot,
-                          bias, vd);
+                          bias, vd, nv);
 }
 
 template <typename T>
 int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,
-                             int nkv, int d, float scale, int window, int vd, float softcap, int chunk, int sink,
-                             cudaStream_t stream) {
+                             int nkv, int d, float scale, int window, int vd, float softcap, int chunk, int sink, int nv,
+                             int out_f32, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vd <= 0) vd = d;
+    if (nv <= 0) nv = nkv;
+    if (nkv <= 0 || nkv % nv != 0) return Q3_ERR_BAD_SIZE;
     if (d <= 0 || d > MAX_HEAD_DIM || vd > MAX_HEAD_DIM || nq <= 0 || nkv <= 0 || nq % nkv != 0) return Q3_ERR_BAD_SIZE;
     if (window > 0 && chunk > 0) return Q3_ERR_BAD_SIZE;
     if (n_tokens > 65535) return Q3_ERR_TOO_LARGE;
     const dim3 grid(nq, (unsigned)n_tokens);
     return (int)q3_launch(attention_generic_kernel<T>, grid, dim3(128), 0, stream, q, k_pages, v_pages, out, token_seq,
-                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window, vd, softcap, chunk, sink);
+                          token_pos, page_table, pages_per_seq, nq, nkv, d, scale, window, vd, softcap, chunk, sink, nv, out_f32);
 }
 
 }  // namespace
@@ -352,19 +360,20 @@ int attention_generic_launch(const T* q, const T* k_pages, const T* v_pages, T* 
                                           const float* sin_tab, const int* token_seq, const int* token_pos,           \
                                           const int* page_table, int pages_per_seq, int64_t n_tokens, int nq,         \
                                           int nkv, int d, float eps, int write_kv, int rotary_dim,           \
-                                          const float* bias, int value_dim, void* stream) {                           \
+                                          const float* bias, int value_dim, int value_heads, void* stream) {          \
         return qkv_prepare_launch<T>((const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, q_norm_w, k_norm_w, cos_tab, \
                                      sin_tab, token_seq, token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d,  \
-                                     eps, write_kv, rotary_dim, bias, value_dim, (cudaStream_t)stream);               \
+                                     eps, write_kv, rotary_dim, bias, value_dim, value_heads, (cudaStream_t)stream);  \
     }                                                                                                                 \
     Q3_EXPORT int q3_attention_generic_##SUFFIX(const void* q, const void* k_pages, const void* v_pages, void* out,   \
                                                 const int* token_seq, const int* token_pos, const int* page_table,    \
                                                 int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,          \
                                                 float scale, int window, int value_dim, float softcap,     \
-                                                int chunk, int sink, void* stream) {                                  \
+                                                int chunk, int sink, int value_heads, int out_f32, void* stream) {    \
         return attention_generic_launch<T>((const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_seq,     \
                                            token_pos, page_table, pages_per_seq, n_tokens, nq, nkv, d, scale, window, \
-                                           value_dim, softcap, chunk, sink, (cudaStream_t)stream);                    \
+                                           value_dim, softcap, chunk, sink, value_heads, out_f32,                     \
+                                           (cudaStream_t)stream);                                                     \
     }
 
 Q3_ATTENTION_EXPORTS(f32, float)

@@ -336,5 +336,34 @@ Q3_EXPORT int q3_place_rows(const void* src, int src_kind, void* dst, int dst_ki
         return gather_rows_launch<T>((const T*)x, (const T*)delta, idx, (T*)out, rows, size, (cudaStream_t)stream); \
     }
 
+// ---------------------------------------------------------------- an activation alone (a feed-forward without a gate)
+// act 0: SiLU, 1: the tanh form of GELU, 2: GELU with the error function, 0.5 z (1 + erf(z / sqrt 2)).
+namespace {
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float z = to_f32<T>(x[i]);
+        float y;
+        if (act == 2) y = 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+        else if (act == 1) y = gate_activation<2>(z);
+        else y = gate_activation<1>(z);
+        out[i] = from_f32<T>(y);
+    }
+}
+}  // namespace
+
+#define Q3_ACTIVATION_EXPORTS(SUFFIX, T)                                                                            \
+    Q3_EXPORT int q3_activation_##SUFFIX(const void* x, void* out, int64_t n, int act, void* stream) {              \
+        if (n <= 0) return 0;                                                                                       \
+        if (act < 0 || act > 2) return Q3_ERR_BAD_SIZE;                                                             \
+        const int64_t blocks = (n + 255) / 256;                                                                     \
+        return (int)q3_launch(activation_kernel<T>, dim3((unsigned)(blocks < 65536 ? blocks : 65536)), dim3(256), 0, \
+                              (cudaStream_t)stream, (const T*)x, (T*)out, n, act);                                  \
+    }
+
 Q3_ELEMENTWISE_EXPORTS(f32, float)
 Q3_ELEMENTWISE_EXPORTS(bf16, bf16)
+Q3_ACTIVATION_EXPORTS(f32, float)
+Q3_ACTIVATION_EXPORTS(bf16, bf16)

@@ -1,0 +1,143 @@
+// Kernels for a hidden state that travels as S streams per token (hyper-connections), kept in
+// 32-bit whatever the compute type T of the matrix products.  Layout: streams [token, S, hidden].
+//
+//   embedding_streams : streams[t][s] = table[ids[t]] * scale for every s                  (T -> float)
+//   hyper_norm        : ONE pass over a token's streams that
+//                         (1) settles the sublayer output y that is still pending,
+//                               x_to <- sum_from mix[from][to] x_from + out[to] y      (all streams at once),
+//                         (2) forms the next sublayer's input u = sum_s in[s] x_s,
+//                         (3) normalises it, r = u / sqrt(mean(u^2) + eps) * w, and rounds r to T.
+//                       Any of the three may be left out: no pending output (the first sublayer), no
+//                       result (settle only), no normalisation (u itself is written).  With `rows` the
+//                       kernel works on the listed tokens only and leaves the streams as they are: the
+//                       model's tail, where only the wanted rows are summed and normalised.
+//
+// S = 1 with mix = [1] and in = [1] is the plain residual sum x <- x + out y.  Coefficients, sums
+// and statistics are 32-bit; only the result is rounded.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_STREAMS = 8;
+
+template <typename T>
+__global__ void embedding_streams_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
+                                         int hidden, int vocab, float scale, int copies) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;                 // an id outside the table gives zero rows
+    const T* src = table + (int64_t)(ok ? id : 0) * hidden;
+    float* dst = out + t * copies * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = ok ? to_f32<T>(src[c]) * scale : 0.0f;
+        for (int s = 0; s < copies; ++s) dst[(int64_t)s * hidden + c] = v;
+    }
+}
+
+// One block per row of the result.  The sum u of a token is kept in shared memory between the two passes.
+template <typename T, typename TO>
+__global__ void hyper_norm_kernel(float* __restrict__ streams, const T* __restrict__ branch, const float* __restrict__ mix,
+                                  const float* __restrict__ out_coef, const float* __restrict__ in_coef,
+                                  const float* __restrict__ norm_w, float eps, TO* __restrict__ out,
+                                  const int* __restrict__ rows, int S, int hidden, int normalize) {
+    extern __shared__ float u_s[];
+    __shared__ float scratch[33];
+    __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t r = blockIdx.x;
+    const int64_t t = rows != nullptr ? rows[r] : r;
+    const bool write_streams = rows == nullptr && branch != nullptr;
+    if (threadIdx.x < S * S && branch != nullptr) c_mix[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < S) {
+        c_out[threadIdx.x] = branch != nullptr ? out_coef[threadIdx.x] : 0.0f;
+        c_in[threadIdx.x] = in_coef != nullptr ? in_coef[threadIdx.x] : 1.0f;
+    }
+    __syncthreads();
+    float* xs = streams + t * S * hidden;
+    const T* y = branch != nullptr ? branch + t * hidden : nullptr;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float x[MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s) x[s] = s < S ? xs[(int64_t)s * hidden + c] : 0.0f;
+        float u = 0.0f;
+        if (y != nullptr) {
+            const float yv = to_f32<T>(y[c]);
+#pragma unroll
+            for (int to = 0; to < MAX_STREAMS; ++to) {
+                if (to < S) {
+                    float v = 0.0f;
+#pragma unroll
+                    for (int from = 0; from < MAX_STREAMS; ++from)
+                        if (from < S) v = fmaf(c_mix[from * S + to], x[from], v);
+                    v = fmaf(c_out[to], yv, v);
+                    if (write_streams) xs[(int64_t)to * hidden + c] = v;
+                    u = fmaf(c_in[to], v, u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+                if (s < S) u = fmaf(c_in[s], x[s], u);
+        }
+        if (out != nullptr) {
+            u_s[c] = u;
+            sq += u * u;
+        }
+    }
+    if (out == nullptr) return;
+    TO* o = out + r * hidden;
+    if (!normalize) {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<TO>(u_s[c]);     // the thread's own writes
+        return;
+    }
+    const float inv = rsqrtf(block_sum(sq, scratch) / (float)hidden + eps);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<TO>(u_s[c] * inv * norm_w[c]);
+}
+
+template <typename T, typename TO>
+int hyper_norm_launch(float* streams, const T* branch, const float* mix, const float* out_coef, const float* in_coef,
+                      const float* norm_w, float eps, TO* out, const int* rows, int64_t n_rows, int S, int hidden, int normalize,
+                      cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (S <= 0 || S > MAX_STREAMS || hidden <= 0 || n_rows > 0x7fffffffLL) return Q3_ERR_BAD_SIZE;
+    if (branch != nullptr && (mix == nullptr || out_coef == nullptr)) return Q3_ERR_BAD_SIZE;
+    if (out != nullptr && normalize && norm_w == nullptr) return Q3_ERR_BAD_SIZE;
+    const size_t smem = out != nullptr ? (size_t)hidden * sizeof(float) : 0;
+    if (smem > 200 * 1024) return Q3_ERR_BAD_SIZE;
+    static Q3PerDevice allowed;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = q3_allow_shared_memory(hyper_norm_kernel<T, TO>, 200 * 1024, allowed);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    return (int)q3_launch(hyper_norm_kernel<T, TO>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
+                          out_coef, in_coef, norm_w, eps, out, rows, S, hidden, normalize);
+}
+
+}  // namespace
+
+#define Q3_HYPER_EXPORTS(SUFFIX, T)                                                                                       \
+    Q3_EXPORT int q3_embedding_streams_##SUFFIX(const int* ids, const void* table, float* out, int64_t n_tokens, int hidden, \
+                                                int vocab, float scale, int copies, void* stream) {                      \
+        if (n_tokens <= 0) return 0;                                                                                      \
+        if (hidden <= 0 || copies <= 0 || n_tokens > 0x7fffffffLL) return Q3_ERR_BAD_SIZE;                                \
+        return (int)q3_launch(embedding_streams_kernel<T>, dim3((unsigned)n_tokens), dim3(hidden >= 1024 ? 256 : 128), 0, \
+                              (cudaStream_t)stream, ids, (const T*)table, out, hidden, vocab, scale, copies);             \
+    }                                                                                                                     \
+    Q3_EXPORT int q3_hyper_norm_##SUFFIX(float* streams, const void* branch, const float* mix, const float* out_coef,     \
+                                         const float* in_coef, const float* norm_w, float eps, void* out, int out_f32,    \
+                                         const int* rows, int64_t n_rows, int n_streams, int hidden, int normalize,       \
+                                         void* stream) {                                                                  \
+        if (out_f32)                                                                                                      \
+            return hyper_norm_launch<T, float>(streams, (const T*)branch, mix, out_coef, in_coef, norm_w, eps, (float*)out, \
+                                               rows, n_rows, n_streams, hidden, normalize, (cudaStream_t)stream);         \
+        return hyper_norm_launch<T, T>(streams, (const T*)branch, mix, out_coef, in_coef, norm_w, eps, (T*)out, rows,     \
+                                       n_rows, n_streams, hidden, normalize, (cudaStream_t)stream);                       \
+    }
+
+Q3_HYPER_EXPORTS(f32, float)
+Q3_HYPER_EXPORTS(bf16, bf16)

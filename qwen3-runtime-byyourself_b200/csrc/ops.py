@@ -381,50 +381,214 @@ def _rotary_dim(cos, sin, d: int) -> int:
 
 def qkv_prepare(qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, cos, sin, token_seq, token_pos, page_table,
                 n_tokens: int, nq: int, nkv: int, d: int, eps: float, write_kv: bool = True, bias=None,
-                value_dim: Optional[int] = None):
+                value_dim: Optional[int] = None, value_heads: Optional[int] = None):
     """Per-head norm of q and k, rotation, and the write of k and v into the cache pages
     (`write_kv=False`: only q is prepared, for a layer that reads another layer's cache).  `bias` (float32, one
-    value per column of the projection) is added first; `value_dim` is the size of a value head if not `d`."""
+    value per column of the projection) is added first; `value_dim` is the size of a value head if not `d`,
+    `value_heads` their number if not `nkv` (values that several key heads share)."""
     s = _suffix(qkv)
-    vd = int(value_dim or d)
+    vd, nv = int(value_dim or d), int(value_heads or nkv)
     if not 0 < d <= 256 or not 0 < vd <= 256 or (d % 2 != 0 and cos is not None and 2 * cos.shape[-1] == d):
         raise KernelError(f"head_dim {d} / value_dim {vd} is not supported: sizes up to 256, an even number of rotated values")
-    if qkv.shape[-1] != (nq + nkv) * d + nkv * vd or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) \
-            or v_pages.shape[1:] != (nkv, PAGE_TOKENS, vd) or (bias is not None and bias.numel() != qkv.shape[-1]):
+    if qkv.shape[-1] != (nq + nkv) * d + nv * vd or k_pages.dtype != qkv.dtype or k_pages.shape[1:] != (nkv, PAGE_TOKENS, d) \
+            or v_pages.shape[1:] != (nv, PAGE_TOKENS, vd) or nkv % nv or (bias is not None and bias.numel() != qkv.shape[-1]):
         raise KernelError("qkv_prepare: shapes do not fit")
     rot = _rotary_dim(cos, sin, d)
     fn = _fn("attention.cu", f"q3_qkv_prepare_{s}",
-             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p])
+             [c_void_p] * 11 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
     _check(fn(_dev(qkv, "qkv"), _dev(q_out, "q_out", qkv.dtype), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
               _ptr(q_norm_w, "q_norm_w", torch.float32), _ptr(k_norm_w, "k_norm_w", torch.float32),
               _ptr(cos, "cos", torch.float32), _ptr(sin, "sin", torch.float32),
               _dev(token_seq, "token_seq", torch.int32), _dev(token_pos, "token_pos", torch.int32),
               _dev(page_table, "page_table", torch.int32), page_table.shape[-1], n_tokens, nq, nkv, d, float(eps),
-              int(bool(write_kv)), rot, _ptr(bias, "bias", torch.float32), vd, _stream()), "qkv_prepare")
+              int(bool(write_kv)), rot, _ptr(bias, "bias", torch.float32), vd, nv, _stream()), "qkv_prepare")
     return q_out
 
 
 def attention_generic(q, k_pages, v_pages, out, token_seq, token_pos, page_table, n_tokens: int, nq: int, nkv: int,
                       d: int, scale: float, window: Optional[int] = None, value_dim: Optional[int] = None,
-                      softcap: float = 0.0, chunk: Optional[int] = None, sink: bool = False):
+                      softcap: float = 0.0, chunk: Optional[int] = None, sink: bool = False, value_heads: Optional[int] = None):
     """Causal grouped-query attention of every token of the step over its sequence's pages.  `softcap` > 0 caps the
     scores smoothly (s <- softcap * tanh(s / softcap)); `chunk`: a query reads only the keys of its own chunk of that
     many positions; `sink`: one more term exp(0), without a value, in the softmax's denominator; `value_dim`: the
-    size of a value head (and of an output head) if not `d`."""
+    size of a value head (and of an output head) if not `d`; `value_heads`: the number of value heads if not `nkv`
+    (each serves nkv / value_heads key heads).  `out` has q's type, or is float32 for a caller that goes on in 32-bit."""
     s = _suffix(q)
-    vd = int(value_dim or d)
+    vd, nv = int(value_dim or d), int(value_heads or nkv)
+    if out.dtype not in (q.dtype, torch.float32) or nkv % nv:
+        raise KernelError("attention: the output has the query's type or float32; key heads are a multiple of value heads")
     if not 0 < d <= 256 or not 0 < vd <= 256:
         raise KernelError(f"head_dim {d} / value_dim {vd} is not supported: sizes up to 256")
     if window and chunk:
         raise KernelError("attention: a window or chunks, not both")
     fn = _fn("attention.cu", f"q3_attention_generic_{s}",
-             [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_int, c_int, c_void_p])
+             [c_void_p] * 7 + [c_int, c_int64, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+                               c_void_p])
     _check(fn(_dev(q, "q"), _dev(k_pages, "k_pages", q.dtype), _dev(v_pages, "v_pages", q.dtype),
-              _dev(out, "out", q.dtype), _dev(token_seq, "token_seq", torch.int32),
+              _dev(out, "out"), _dev(token_seq, "token_seq", torch.int32),
               _dev(token_pos, "token_pos", torch.int32), _dev(page_table, "page_table", torch.int32),
               page_table.shape[-1], n_tokens, nq, nkv, d, float(scale), int(window or 0), vd, float(softcap or 0.0),
-              int(chunk or 0), int(bool(sink)), _stream()),
+              int(chunk or 0), int(bool(sink)), nv, int(out.dtype == torch.float32 and q.dtype != torch.float32), _stream()),
            "attention_generic")
+    return out
+
+
+# ------------------------------------------------------------------ several streams of hidden state (hyper-connections)
+def embedding_streams(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float, copies: int) -> torch.Tensor:
+    """out[t] = `copies` times table[ids[t]] * scale side by side, as float32: out [N, copies * hidden]."""
+    n = ids.numel()
+    if out.shape[0] < n or out.shape[1] != copies * table.shape[1] or out.dtype != torch.float32:
+        raise KernelError("embedding_streams: output does not fit")
+    fn = _fn("hyper.cu", f"q3_embedding_streams_{_suffix(table)}",
+             [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_dev(ids, "ids", torch.int32), _dev(table, "table"), _dev(out, "out"), n, table.shape[1], table.shape[0],
+              float(scale), int(copies), _stream()), "embedding_streams")
+    return out
+
+
+def hyper_norm(streams: torch.Tensor, n_streams: int, branch: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+               out_coef: Optional[torch.Tensor], in_coef: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float,
+               out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+               normalize: bool = True, compute_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """One pass over the streams [N, n_streams * hidden] (float32) of every token: settle a pending sublayer output
+    `branch` [N, hidden] (x_to <- sum_from mix[from, to] x_from + out_coef[to] branch), form u = sum_s in_coef[s] x_s
+    (None: ones) and write out = u / sqrt(mean(u^2) + eps) * norm_w (`normalize=False`: u itself).  `branch` and `out`
+    may each be None.  With `rows` (int32 token numbers) only those tokens are worked on, `out` has one row for each
+    and the streams are left as they are.  `out` has the compute type (the branch's) or float32."""
+    N, width = streams.shape
+    hidden = width // n_streams
+    ref = branch if branch is not None else out
+    if ref is None:
+        return None
+    kind = compute_dtype or (branch.dtype if branch is not None else out.dtype)
+    count = int(n_rows if n_rows is not None else (rows.numel() if rows is not None else N))
+    if width != hidden * n_streams or (branch is not None and tuple(branch.shape) != (N, hidden)) \
+            or (out is not None and (out.shape[0] < count or out.shape[1] != hidden or out.dtype not in (kind, torch.float32))):
+        raise KernelError("hyper_norm: shapes do not fit")
+    fn = _fn("hyper.cu", f"q3_hyper_norm_{_SUFFIX[kind]}",
+             [c_void_p] * 6 + [c_float, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(streams, "streams", torch.float32), _ptr(branch, "branch", kind), _ptr(mix, "mix", torch.float32),
+              _ptr(out_coef, "out_coef", torch.float32), _ptr(in_coef, "in_coef", torch.float32),
+              _ptr(norm_w, "norm_w", torch.float32), float(eps), _ptr(out, "out"),
+              int(out is not None and out.dtype == torch.float32 and kind != torch.float32), _ptr(rows, "rows", torch.int32),
+              count, int(n_streams), hidden, int(bool(normalize)), _stream()), "hyper_norm")
+    return out
+
+
+# ------------------------------------------------------------------ linear attention with a decay and a state per sequence
+def lightning_attention(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, seq_start: torch.Tensor,
+                        seq_slots: torch.Tensor, out: torch.Tensor, n_seqs: int, heads: int, d: int, vd: int,
+                        chunked: bool = False) -> torch.Tensor:
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over the new tokens of every sequence, from and to the state rows
+    [slot, heads, d, vd] (float32).  `proj` [N, 2 heads d + 2 heads vd] holds q, k, v (SiLU is applied here) and a gate
+    that is not read; `out` [N, heads * vd] float32.  `chunked`: the form for prompts (32 tokens at a time)."""
+    if proj.shape[1] != 2 * heads * (d + vd) or tuple(state.shape[1:]) != (heads, d, vd) or out.shape[1] != heads * vd \
+            or out.dtype != torch.float32 or decay.numel() != heads:
+        raise KernelError("lightning_attention: shapes do not fit")
+    name = "chunks" if chunked else "scan"
+    fn = _fn("lightning.cu", f"q3_lightning_{name}_{_suffix(proj)}", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(proj, "proj"), _dev(state, "state", torch.float32), _dev(decay, "decay", torch.float32),
+              _dev(seq_start, "seq_start", torch.int32), _dev(seq_slots, "seq_slots", torch.int32), _dev(out, "out"),
+              int(n_seqs), heads, d, vd, _stream()), f"lightning_{name}")
+    return out
+
+
+def lightning_chunks_fit(d: int, vd: int) -> bool:
+    """Whether the chunked form's buffers fit in an SM's shared memory for these head sizes."""
+    R = min(d, 1024 // vd)
+    return (2 * 32 * (d + 1) + 32 * vd + 32 * 33 + R * 32 * vd) * 4 <= 200 * 1024
+
+
+def gated_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate), row by row; o float32 [N, size], `gate` a view of
+    [N, size] columns (its row stride may be larger), out in the compute type."""
+    N, size = o.shape
+    if gate.shape != o.shape or gate.stride(1) != 1 or out.shape != o.shape or gate.dtype != out.dtype or not out.is_contiguous():
+        raise KernelError("gated_norm: shapes do not fit")
+    fn = _fn("lightning.cu", f"q3_gated_norm_{_suffix(out)}", [c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int, c_void_p])
+    _check(fn(_dev(o, "o", torch.float32), gate.data_ptr(), gate.stride(0), _dev(weight, "weight", torch.float32), float(eps),
+              out.data_ptr(), N, size, _stream()), "gated_norm")
+    return out
+
+
+# ------------------------------------------------------------------ differential attention
+def diff_combine(a: torch.Tensor, out: torch.Tensor, n_tokens: int, heads: int, per_group: int, vd: int, lam: float, eps: float,
+                 gain: float) -> torch.Tensor:
+    """out[t, h] = unit_rms(a1 - lam * a2) * gain over vd values; `a` float32 [N, groups, 2 maps, per_group, vd]."""
+    if a.dtype != torch.float32 or a.numel() < n_tokens * 2 * heads * vd or out.numel() < n_tokens * heads * vd:
+        raise KernelError("diff_combine: shapes do not fit")
+    fn = _fn("differential.cu", f"q3_diff_combine_{_suffix(out)}",
+             [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    _check(fn(_dev(a, "a"), _dev(out, "out"), n_tokens, heads, per_group, vd, float(lam), float(eps), float(gain), _stream()),
+           "diff_combine")
+    return out
+
+
+# ------------------------------------------------------------------ feed-forwards: a plain activation; routed experts
+PLAIN_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "gelu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(x) elementwise (`out` may be `x`); kinds: silu, gelu_tanh, gelu (with the error function)."""
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("activation: output does not fit")
+    fn = _fn("elementwise.cu", f"q3_activation_{_suffix(x)}", [c_void_p, c_void_p, c_int64, c_int, c_void_p])
+    _check(fn(_dev(x, "x"), _dev(out, "out"), x.numel(), PLAIN_ACTIVATIONS[kind], _stream()), "activation")
+    return out
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, top_ids: torch.Tensor, top_w: torch.Tensor,
+              id_weight: torch.Tensor, n_real: int, top: int, group_count: int = 1, group_keep: int = 1) -> None:
+    """Router of a mixture of experts for every token of h [N, hidden]: float32 logits, softmax over all outputs,
+    choice by score + correction within the kept groups, weights = plain scores; see csrc/moe.cu."""
+    N, hidden = h.shape
+    n_out = w_router.shape[0]
+    if w_router.shape[1] != hidden or w_router.dtype != h.dtype or correction.numel() != n_out or top_ids.numel() < N * top \
+            or top_w.numel() < N * top or id_weight.numel() < N:
+        raise KernelError("moe_route: shapes do not fit")
+    fn = _fn("moe.cu", f"q3_moe_route_{_suffix(h)}", [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_dev(h, "h"), _dev(w_router, "w_router"), _dev(correction, "correction", torch.float32),
+              _dev(top_ids, "top_ids", torch.int32), _dev(top_w, "top_w", torch.float32), _dev(id_weight, "id_weight", torch.float32),
+              N, hidden, n_out, int(n_real), int(top), int(group_count), int(group_keep), _stream()), "moe_route")
+
+
+def moe_sort(top_ids: torch.Tensor, n_pairs: int, n_real: int, offsets: torch.Tensor, slot_of_pair: torch.Tensor,
+             pair_of_slot: torch.Tensor) -> None:
+    """Lays the (token, choice) pairs out expert by expert: offsets [n_real + 1], a slot for every pair (-1: an
+    identity expert) and the pair of every slot."""
+    if offsets.numel() < n_real + 1 or slot_of_pair.numel() < n_pairs or pair_of_slot.numel() < n_pairs:
+        raise KernelError("moe_sort: shapes do not fit")
+    fn = _fn("moe.cu", "q3_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_dev(top_ids, "top_ids", torch.int32), int(n_pairs), int(n_real), _dev(offsets, "offsets", torch.int32),
+              _dev(slot_of_pair, "slot_of_pair", torch.int32), _dev(pair_of_slot, "pair_of_slot", torch.int32), _stream()), "moe_sort")
+
+
+def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
+                act: torch.Tensor, y: torch.Tensor, n_pairs: int, n_real: int, top: int, ff: int, limit: float, alpha: float) -> None:
+    """The experts' two products for the sorted pairs: act[slot] = g sigmoid(alpha g) (u + 1) with g = min(W_gate x, limit),
+    u = clamp(W_up x, -limit, limit), then y[slot] = W_down act[slot] (float32).  w_gate_up [n_real, 2 ff, hidden] (an
+    expert's gate rows, then its up rows), w_down [n_real, hidden, ff]."""
+    hidden = h.shape[1]
+    if w_gate_up.numel() != n_real * 2 * ff * hidden or w_down.numel() != n_real * hidden * ff or act.numel() < n_pairs * ff \
+            or y.numel() < n_pairs * hidden or y.dtype != torch.float32 or act.dtype != h.dtype or w_gate_up.dtype != h.dtype:
+        raise KernelError("moe_experts: shapes do not fit")
+    fn = _fn("moe.cu", f"q3_moe_experts_{_suffix(h)}", [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(_dev(h, "h"), _dev(w_gate_up, "w_gate_up"), _dev(w_down, "w_down"), _dev(offsets, "offsets", torch.int32),
+              _dev(pair_of_slot, "pair_of_slot", torch.int32), _dev(act, "act"), _dev(y, "y"), int(n_pairs), int(n_real), int(top),
+              hidden, int(ff), float(limit), float(alpha), _stream()), "moe_experts")
+    _count_extra(1)
+
+
+def moe_combine(y: torch.Tensor, h: torch.Tensor, slot_of_pair: torch.Tensor, top_w: torch.Tensor, id_weight: torch.Tensor,
+                out: torch.Tensor, top: int) -> torch.Tensor:
+    """out[t] = sum_k top_w[t, k] y[slot_of_pair[t, k]] + id_weight[t] h[t]."""
+    N, hidden = h.shape
+    if out.shape != h.shape or out.dtype != h.dtype:
+        raise KernelError("moe_combine: shapes do not fit")
+    fn = _fn("moe.cu", f"q3_moe_combine_{_suffix(h)}", [c_void_p] * 6 + [c_int64, c_int, c_int, c_void_p])
+    _check(fn(_dev(y, "y", torch.float32), _dev(h, "h"), _dev(slot_of_pair, "slot_of_pair", torch.int32),
+              _dev(top_w, "top_w", torch.float32), _dev(id_weight, "id_weight", torch.float32), _dev(out, "out"), N, int(top), hidden,
+              _stream()), "moe_combine")
     return out
 
 

@@ -39,6 +39,10 @@ FUSED_DECODE_KERNELS = []
 # Kernels that do the q/k/v product of a prompt step themselves, with norm, rotation and cache write in its
 # epilogue: fn(part, x, cache, q, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool (q is filled, the pages written)
 FUSED_PROJECTION_KERNELS = []
+# Kernels for parts that only the general kernel serves otherwise (`general_only`): they take the projection output
+# as it is and do the per-head norms, the cache write and the attention of any step themselves:
+# fn(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps) -> bool
+RAW_KERNELS = []
 
 
 TENSOR_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
@@ -51,7 +55,7 @@ class GQAAttention(Part):
                  qk_norm: Optional[PartSpec] = None, position: Optional[PartSpec] = None,
                  window: Optional[int] = None, prefix: str = "", value_dim: Optional[int] = None, bias: bool = False,
                  softcap: Optional[float] = None, chunk: Optional[int] = None, sink: bool = False,
-                 names: Optional[dict] = None):
+                 names: Optional[dict] = None, value_heads: Optional[int] = None, out_float32: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         value_dim = int(value_dim or head_dim)
@@ -63,6 +67,13 @@ class GQAAttention(Part):
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.scale, self.window, self.prefix = float(scale), window, prefix
         self.value_dim, self.has_bias, self.sink = value_dim, bool(bias), bool(sink)
+        # values that several key heads share (`value_heads` < num_kv_heads), and an output that stays in 32-bit for
+        # a part that goes on with it (`out_float32`): both are served by the general kernel only
+        self.value_heads = int(value_heads or num_kv_heads)
+        if num_kv_heads % self.value_heads:
+            raise ValueError("num_kv_heads must be a multiple of value_heads")
+        self.out_float32 = bool(out_float32)
+        self.general_only = self.value_heads != num_kv_heads or self.out_float32
         self.softcap = float(softcap) if softcap else 0.0
         self.chunk = int(chunk) if chunk else None
         self.names = dict(TENSOR_NAMES, **(names or {}))
@@ -72,21 +83,26 @@ class GQAAttention(Part):
         self.w_qkv = self.w_o = self.bias = None
         self.reordered = False       # the rows of the q and k projections follow the position encoding's kernel order
         # what the kernels written for Qwen3's attention take
-        self.plain = not (self.has_bias or self.softcap or self.chunk or self.sink or value_dim != head_dim or head_dim % 16)
+        self.plain = not (self.has_bias or self.softcap or self.chunk or self.sink or value_dim != head_dim or head_dim % 16
+                          or self.general_only)
 
     # -- weights
     def weight_specs(self, prefix: str) -> dict:
         p, n = prefix + self.prefix, self.names
-        nq, nkv, d, vd, H = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.hidden_size
+        nq, nkv, d, vd, H, nv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.hidden_size, self.value_heads
         specs = {p + n["q"]: WeightSpec((nq * d, H)), p + n["k"]: WeightSpec((nkv * d, H)),
-                 p + n["v"]: WeightSpec((nkv * vd, H)), p + n["o"]: WeightSpec((H, nq * vd))}
+                 p + n["v"]: WeightSpec((nv * vd, H)), p + n["o"]: WeightSpec((H, self.output_width()))}
         if self.has_bias:
             specs.update({p + n["q_bias"]: WeightSpec((nq * d,), "bias"), p + n["k_bias"]: WeightSpec((nkv * d,), "bias"),
-                          p + n["v_bias"]: WeightSpec((nkv * vd,), "bias")})
+                          p + n["v_bias"]: WeightSpec((nv * vd,), "bias")})
         if self.q_norm is not None:
             specs.update(self.q_norm.weight_specs(p + n["q_norm"]))
             specs.update(self.k_norm.weight_specs(p + n["k_norm"]))
         return specs
+
+    def output_width(self) -> int:
+        """Columns of the output projection: what the attention hands to it per token."""
+        return self.num_heads * self.value_dim
 
     def bind(self, weights: dict, prefix: str, dtype, device) -> None:
         p, n = prefix + self.prefix, self.names
@@ -118,15 +134,21 @@ class GQAAttention(Part):
     def cache_need(self) -> CacheNeed:
         kind = "window" if self.window else ("chunk" if self.chunk else "full")
         return CacheNeed(kind, self.num_kv_heads, self.head_dim, self.window or self.chunk,
-                         value_dim=self.value_dim if self.value_dim != self.head_dim else None)
+                         value_dim=self.value_dim if self.value_dim != self.head_dim else None,
+                         value_heads=self.value_heads if self.value_heads != self.num_kv_heads else None)
 
     # -- step
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        out = ctx.scratch.get("mixer.out", (ctx.n_tokens, self.hidden_size), ctx.dtype)
+        return linear(self.mix(x, ctx, cache), self.w_o, out)
+
+    def mix(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        """Everything before the output projection: [N, num_heads * value_dim] in the compute type (float32 with
+        `out_float32`)."""
         nq, nkv, d, vd = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
         N = ctx.n_tokens
         table = ctx.page_tables[cache.group]
-        attn = ctx.scratch.get("attn.ctx", (N, nq * vd), ctx.dtype)
-        out = ctx.scratch.get("mixer.out", (N, self.hidden_size), ctx.dtype)
+        attn = ctx.scratch.get("attn.ctx", (N, nq * vd), torch.float32 if self.out_float32 else ctx.dtype)
         norm_eps = self.q_norm.eps if self.q_norm is not None else 0.0
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
@@ -135,35 +157,42 @@ class GQAAttention(Part):
         if tables and self.position is not None:
             self.position.prepare(ctx.max_positions, ctx.device)
             cos, sin = self.position.cos, self.position.sin
-        if tables and not ctx.is_decode and ctx.dtype == torch.bfloat16:
+        special = ctx.dtype == torch.bfloat16 and not self.general_only
+        if tables and not ctx.is_decode and special:
             q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
             for kernel in FUSED_PROJECTION_KERNELS:
                 if kernel(self, x, cache, q, ctx, table, qw, kw, norm_eps, cos, sin):
                     self.attend(q, cache, attn, ctx, table)
-                    return linear(attn, self.w_o, out)
-        qkv = ctx.scratch.get("attn.qkv", (N, (nq + nkv) * d + nkv * vd), ctx.dtype)
+                    return attn
+        qkv = ctx.scratch.get("attn.qkv", (N, (nq + nkv) * d + self.value_heads * vd), ctx.dtype)
         linear(x, self.w_qkv, qkv)
-        if tables and ctx.is_decode and ctx.dtype == torch.bfloat16:
+        if tables and ctx.is_decode and special:
             for kernel in FUSED_DECODE_KERNELS:
                 if kernel(self, qkv, cache, attn, ctx, table, qw, kw, norm_eps, cos, sin):
-                    return linear(attn, self.w_o, out)
+                    return attn
+        if tables and ctx.dtype == torch.bfloat16:
+            for kernel in RAW_KERNELS:                    # kernels of parts that take the projection output as it is
+                if kernel(self, qkv, cache, attn, ctx, table, qw, kw, norm_eps):
+                    return attn
         q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
         if tables:
             ops.qkv_prepare(qkv, q, cache.keys, cache.values, qw, kw, cos, sin, ctx.token_seq, ctx.token_pos, table,
-                            N, nq, nkv, d, norm_eps, write_kv=not cache.shared, bias=self.bias, value_dim=vd)
+                            N, nq, nkv, d, norm_eps, write_kv=not cache.shared, bias=self.bias, value_dim=vd,
+                            value_heads=self.value_heads)
         else:
             self._prepare_unfused(qkv, q, cache, ctx, table, qw, kw, norm_eps)
         self.attend(q, cache, attn, ctx, table)
-        return linear(attn, self.w_o, out)
+        return attn
 
     def attend(self, q, cache, out, ctx, table) -> None:
-        if ctx.dtype == torch.bfloat16:
+        if ctx.dtype == torch.bfloat16 and not self.general_only:
             for kernel in (DECODE_KERNELS if ctx.is_decode else PREFILL_KERNELS):
                 if kernel(self, q, cache, out, ctx, table):
                     return
         ops.attention_generic(q, cache.keys, cache.values, out, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
                               self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
-                              value_dim=self.value_dim, softcap=self.softcap, chunk=self.chunk, sink=self.sink)
+                              value_dim=self.value_dim, softcap=self.softcap, chunk=self.chunk, sink=self.sink,
+                              value_heads=self.value_heads)
 
     def _prepare_unfused(self, qkv, q, cache, ctx, table, qw, kw, eps) -> None:
         """A position encoding without kernel tables: norm, then `apply_`, then the cache write."""

@@ -100,5 +100,97 @@ class SandwichNormBlock(Part):
         return residual, NormedBranch(self.feed_forward.forward(normed, ctx), self.norms[3])
 
 
+class HyperPending:
+    """A sublayer's output (compute type) that is still to be added to the streams: every stream becomes a mix of the
+    old streams plus its share of the output."""
+
+    def __init__(self, branch, mix, out_coef):
+        self.branch, self.mix, self.out_coef = branch, mix, out_coef
+
+
+class HyperConnectionBlock(Part):
+    """Pre-norm sublayers on a hidden state of `streams` copies per token ([N, streams * hidden], float32).  For
+    sublayer q (1: mixer, 2: feed-forward) with the tensors `hc<q>.in` [s], `hc<q>.out` [s], `hc<q>.mix` [s, s]
+    (indexed [from, to]):
+
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_to <- sum_from mix[from, to] x_from + mult * out[to] * y
+
+    `streams=None` is the plain residual sum x <- x + mult * y on one stream, without those tensors.  The sum is left
+    pending and settled by whoever reads the streams next, in the kernel that forms and normalises its own input,
+    so a sublayer costs one pass over the streams.  `finish` is the model's tail: the sum of the streams of the
+    wanted rows, normalised."""
+    stream_dtype = "float32"
+
+    def __init__(self, mixer, feed_forward, norm: PartSpec, hidden_size: int, streams=None, residual_mult: float = 1.0,
+                 names=("norm1", "norm2"), connection_names=("hc1.", "hc2.")):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.hidden_size, self.streams, self.mult = int(hidden_size), streams, float(residual_mult)
+        self.n_streams = int(streams or 1)
+        self.names, self.connection_names = tuple(names), tuple(connection_names)
+        self.norms = [build_part("norm", norm) for _ in range(2 if feed_forward is not None else 1)]
+        self.coef = []                 # per sublayer: (in [s], mult * out [s], mix [s, s]) float32
+
+    def weight_specs(self, prefix: str) -> dict:
+        from ..weights.loader import WeightSpec
+        specs, s = {}, self.n_streams
+        for part, name in zip(self.norms, self.names):
+            specs.update(part.weight_specs(prefix + name))
+        if self.streams is not None:
+            for c in self.connection_names[:len(self.norms)]:
+                specs.update({prefix + c + "in": WeightSpec((s,), "bias"), prefix + c + "out": WeightSpec((s,), "bias"),
+                              prefix + c + "mix": WeightSpec((s, s), "bias")})
+        specs.update(self.mixer.weight_specs(prefix))
+        if self.feed_forward is not None:
+            specs.update(self.feed_forward.weight_specs(prefix))
+        return specs
+
+    def bind(self, weights: dict, prefix: str, dtype, device) -> None:
+        import torch
+        for part, name in zip(self.norms, self.names):
+            part.bind(weights, prefix + name, dtype, device)
+        self.coef = []
+        if self.streams is not None:
+            raw = [[weights[prefix + c + k] for k in ("in", "out", "mix")] for c in self.connection_names[:len(self.norms)]]
+            getattr(weights, "wait", lambda: None)()          # a streamed checkpoint: the tensors are in place now
+            for into, out, mix in raw:
+                f = dict(device=device, dtype=torch.float32)
+                self.coef.append((into.to(**f).contiguous(), (out.to(**f) * self.mult).contiguous(), mix.to(**f).contiguous()))
+        else:
+            one = torch.ones(1, dtype=torch.float32, device=device)
+            self.coef = [(one, one * self.mult, one.view(1, 1))] * len(self.norms)
+        self.mixer.bind(weights, prefix, dtype, device)
+        if self.feed_forward is not None:
+            self.feed_forward.bind(weights, prefix, dtype, device)
+
+    def _read(self, residual, pending, which: int, ctx):
+        """Settle `pending` and return the normalised input of sublayer `which`."""
+        from ..csrc import ops
+        if pending is not None and not isinstance(pending, HyperPending):
+            raise TypeError("streams take a HyperPending as their pending sum")
+        normed = ctx.scratch.get("block.normed", (residual.shape[0], self.hidden_size), ctx.dtype)
+        norm = self.norms[which]
+        return ops.hyper_norm(residual, self.n_streams, pending.branch if pending else None, pending.mix if pending else None,
+                              pending.out_coef if pending else None, self.coef[which][0], norm.weight, norm.eps, normed)
+
+    def forward(self, residual, delta, ctx, cache):
+        normed = self._read(residual, delta, 0, ctx)
+        pending = HyperPending(self.mixer.forward(normed, ctx, cache), self.coef[0][2], self.coef[0][1])
+        if self.feed_forward is None:
+            return residual, pending
+        normed = self._read(residual, pending, 1, ctx)
+        return residual, HyperPending(self.feed_forward.forward(normed, ctx), self.coef[1][2], self.coef[1][1])
+
+    def finish(self, residual, pending, final_norm, ctx, out, normalize: bool = True):
+        """out[r] = norm(sum of the streams of wanted row r) with the pending sum settled on the way (for these rows
+        only, in registers: nothing reads the streams after the tail).  `normalize=False`: the plain sum."""
+        from ..csrc import ops
+        rows = None if ctx.want_all else ctx.want_rows[:ctx.n_want]
+        dtype = pending.branch.dtype if pending is not None else ctx.dtype
+        return ops.hyper_norm(residual, self.n_streams, pending.branch if pending else None, pending.mix if pending else None,
+                              pending.out_coef if pending else None, None, final_norm.weight, final_norm.eps, out, rows=rows,
+                              n_rows=ctx.n_want, normalize=normalize, compute_dtype=dtype)
+
+
+register_part("block", "hyper_connections", HyperConnectionBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)

@@ -24,8 +24,10 @@ from .linear import linear
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab_size: int, hidden_size: int, scale: Optional[float] = None, tensor: str = "weight"):
-        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+    def __init__(self, vocab_size: int, hidden_size: int, scale: Optional[float] = None, tensor: str = "weight",
+                 copies: int = 1):
+        """`copies` > 1: every token's row is written that many times side by side (out [N, copies * hidden])."""
+        self.vocab_size, self.hidden_size, self.copies = int(vocab_size), int(hidden_size), int(copies)
         self.scale = None if scale is None else float(scale)
         self.tensor = tensor
         self.table = None
@@ -37,6 +39,8 @@ class TokenEmbedding(Part):
         self.table = weights[prefix + self.tensor].contiguous()
 
     def forward(self, token_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        if self.copies > 1:
+            return ops.embedding_streams(token_ids, self.table, out, 1.0 if self.scale is None else self.scale, self.copies)
         if out.dtype == torch.float32 and (self.scale is not None or self.table.dtype != torch.float32):
             return ops.embedding_scaled(token_ids, self.table, out, 1.0 if self.scale is None else self.scale)
         if self.scale is not None:

@@ -65,5 +65,37 @@ class SwiGLU(Part):
         return linear(act, self.w_down, out)
 
 
+class DenseMLP(Part):
+    """A feed-forward without a gate: down( act(up(x)) ); act one of `ops.PLAIN_ACTIVATIONS` (GELU with the error
+    function by default).  The checkpoint names of the two matrices are parameters."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "", activation: str = "gelu",
+                 names: Optional[dict] = None):
+        if activation not in ops.PLAIN_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r}: one of {sorted(ops.PLAIN_ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size, self.prefix = int(hidden_size), int(intermediate_size), prefix
+        self.activation = activation
+        self.names = dict({"up": "up_proj.weight", "down": "down_proj.weight"}, **(names or {}))
+        self.w_up = self.w_down = None
+
+    def weight_specs(self, prefix: str) -> dict:
+        p, H, I, n = prefix + self.prefix, self.hidden_size, self.intermediate_size, self.names
+        return {p + n["up"]: WeightSpec((I, H)), p + n["down"]: WeightSpec((H, I))}
+
+    def bind(self, weights: dict, prefix: str, dtype, device) -> None:
+        p = prefix + self.prefix
+        self.w_up = weights.pop(p + self.names["up"]).contiguous()
+        self.w_down = weights.pop(p + self.names["down"]).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        N = ctx.n_tokens
+        act = ctx.scratch.get("ff.act", (N, self.intermediate_size), ctx.dtype)
+        linear(x, self.w_up, act)
+        ops.activation(act, act, self.activation)
+        out = ctx.scratch.get("ff.out", (N, self.hidden_size), ctx.dtype)
+        return linear(act, self.w_down, out)
+
+
+register_part("feed_forward", "dense_mlp", DenseMLP)
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "gated_mlp", SwiGLU)

@@ -40,6 +40,7 @@ class Model:
         self.dtype: Optional[torch.dtype] = None
         self.device = None
         self._warned_rounding = False
+        self.after_run = None             # a debugging hook: after_run(run, residual, pending, ctx) after every layer run
 
     # -- weights
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -103,7 +104,7 @@ class Model:
         logits [n_want, vocab] for the wanted rows, or None if none is wanted."""
         N, H = ctx.n_tokens, self.plan.hidden_size
         stream_dtype = self.residual_dtype or ctx.dtype
-        residual = ctx.scratch.get("model.residual", (N, H), stream_dtype)
+        residual = ctx.scratch.get("model.residual", (N, self.plan.streams * H), stream_dtype)
         self.embedding.forward(ctx.token_ids[:N], residual)
         x0 = None
         if self.stream_steps:                              # the embedding's output is read again later: keep it
@@ -117,11 +118,16 @@ class Model:
             if step is not None:
                 residual, delta = step[0].forward(residual, delta, x0, ctx)
             residual, delta = self.blocks[index].forward(residual, delta, ctx, cache.layer(self.plan.cache_of_run(run)))
+            if self.after_run is not None:
+                self.after_run(run, residual, delta, ctx)
         if ctx.n_want == 0:
             return None
         R = ctx.n_want
         normed = ctx.scratch.get("model.rows_normed", (R, H), ctx.dtype)
-        if self.residual_dtype is not None:                # a float32 stream: its pending sum and norms have kernels of their own
+        finish = getattr(self.blocks[self.plan.order[-1]], "finish", None)
+        if finish is not None:                             # the block knows how its hidden state travels
+            finish(residual, delta, self.final_norm, ctx, normed)
+        elif self.residual_dtype is not None:                # a float32 stream: its pending sum and norms have kernels of their own
             from .block import settle
             if ctx.want_all:
                 settle(residual, delta, self.final_norm, normed)

@@ -1,0 +1,83 @@
+"""A routed feed-forward (mixture of experts) as a part.
+
+Router: logits z = W_r x in 32-bit, scores s = softmax(z) over all router outputs; the choice is made on
+s + correction (a stored vector), among the experts of the `group_keep` best of `group_count` equal groups of
+neighbours (a group's score: its best choice score); the `top` best are chosen and weighted by their plain
+scores s, not renormalised.  The last `identity` router outputs are experts without tensors whose output is the
+input itself.  An expert: g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit), W_down (g sigmoid(alpha g) (u + 1)).
+
+Nothing on the host depends on how many tokens an expert gets: the pairs (token, choice) are laid out expert by
+expert on the device and the experts' products walk that layout, so a decode step with this part can be captured.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from ..weights.upload import fuse_rows
+from .base import Part, register_part
+
+SIGMOID_ALPHA = 1.702
+
+
+class RoutedExperts(Part):
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, limit: float, identity: int = 0,
+                 group_count: int = 1, group_keep: int = 1, prefix: str = "", alpha: float = SIGMOID_ALPHA,
+                 names: Optional[dict] = None):
+        outputs = experts + identity
+        if not 0 < top <= outputs or outputs % group_count or not 0 < group_keep <= group_count \
+                or group_keep * (outputs // group_count) < top:
+            raise ValueError("routed experts: 0 < top <= experts + identity, groups divide them, the kept groups hold top experts")
+        self.hidden_size, self.intermediate_size, self.prefix = int(hidden_size), int(intermediate_size), prefix
+        self.experts, self.identity, self.top = int(experts), int(identity), int(top)
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.group_count, self.group_keep = int(group_count), int(group_keep)
+        self.names = dict({"router": "router", "correction": "correction", "expert": "e{}.", "gate": "gate", "up": "up",
+                           "down": "down"}, **(names or {}))
+        self.w_router = self.correction = self.w_gate_up = self.w_down = None
+
+    def _expert(self, p: str, e: int, which: str) -> str:
+        return p + self.names["expert"].format(e) + self.names[which]
+
+    def weight_specs(self, prefix: str) -> dict:
+        p, H, I = prefix + self.prefix, self.hidden_size, self.intermediate_size
+        specs = {p + self.names["router"]: WeightSpec((self.experts + self.identity, H)),
+                 p + self.names["correction"]: WeightSpec((self.experts + self.identity,), "bias")}
+        for e in range(self.experts):
+            specs.update({self._expert(p, e, "gate"): WeightSpec((I, H)), self._expert(p, e, "up"): WeightSpec((I, H)),
+                          self._expert(p, e, "down"): WeightSpec((H, I))})
+        return specs
+
+    def bind(self, weights: dict, prefix: str, dtype, device) -> None:
+        p = prefix + self.prefix
+        self.w_router = weights.pop(p + self.names["router"]).contiguous()
+        self.correction = weights[p + self.names["correction"]].to(device=device, dtype=torch.float32).contiguous()
+        if self.experts:
+            # [expert, gate rows then up rows, hidden] and [expert, hidden, ff], each one matrix
+            self.w_gate_up = fuse_rows(weights, [self._expert(p, e, w) for e in range(self.experts) for w in ("gate", "up")])
+            self.w_down = fuse_rows(weights, [self._expert(p, e, "down") for e in range(self.experts)])
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        N, H, I, top = ctx.n_tokens, self.hidden_size, self.intermediate_size, self.top
+        P = N * top
+        s = ctx.scratch
+        top_ids, top_w = s.get("moe.top_ids", (P,), torch.int32), s.get("moe.top_w", (P,), torch.float32)
+        id_weight = s.get("moe.id_weight", (N,), torch.float32)
+        ops.moe_route(x, self.w_router, self.correction, top_ids, top_w, id_weight, self.experts, top, self.group_count,
+                      self.group_keep)
+        offsets = s.get("moe.offsets", (self.experts + 1,), torch.int32)
+        slot_of_pair, pair_of_slot = s.get("moe.slot_of_pair", (P,), torch.int32), s.get("moe.pair_of_slot", (P,), torch.int32)
+        ops.moe_sort(top_ids, P, self.experts, offsets, slot_of_pair, pair_of_slot)
+        y = s.get("moe.y", (P, H), torch.float32)
+        if self.experts:
+            act = s.get("moe.act", (P, I), ctx.dtype)
+            ops.moe_experts(x, self.w_gate_up, self.w_down, offsets, pair_of_slot, act, y, P, self.experts, top, I, self.limit,
+                            self.alpha)
+        out = s.get("ff.out", (N, H), ctx.dtype)
+        return ops.moe_combine(y, x, slot_of_pair, top_w, id_weight, out, top)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -14,16 +14,20 @@ from .base import Part, register_part
 
 
 class RMSNorm(Part):
-    def __init__(self, size: int, eps: float):
-        self.size, self.eps = int(size), float(eps)
+    def __init__(self, size: int, eps: float, one_plus: bool = False):
+        """`one_plus`: the stored weight lies around zero and the norm multiplies by 1 + weight."""
+        self.size, self.eps, self.one_plus = int(size), float(eps), bool(one_plus)
         self.weight = None
 
     def weight_specs(self, name: str) -> dict:
-        return {name: WeightSpec((self.size,), "norm")}
+        return {name: WeightSpec((self.size,), "bias" if self.one_plus else "norm")}
 
     def bind(self, weights: dict, name: str, dtype, device) -> None:
         # a scale vector is used in 32-bit whatever it was stored in (exact for bfloat16)
         self.weight = weights[name].to(device=device, dtype=torch.float32).contiguous()
+        if self.one_plus:
+            getattr(weights, "wait", lambda: None)()          # a streamed checkpoint: the tensor is in place now
+            self.weight = (self.weight + 1.0).contiguous()
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor, delta=None) -> torch.Tensor:
         return ops.rms_norm(x, self.weight, self.eps, out, delta)
