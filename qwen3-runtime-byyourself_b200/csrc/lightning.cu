@@ -6,8 +6,9 @@
 // with q, k, v = SiLU of the projection output.  A row of the projection holds, head by head, the H*d
 // values of q, the H*d of k, the H*vd of v and the H*vd of the output gate g.
 //
-//   lightning_scan  : one block per (head, sequence) walks the sequence's new tokens in order with the
-//                     state in registers: thread (j, r) owns column j of the state and the rows r, r + R,
+//   lightning_scan  : one block per (head, sequence, tile of up to 64 columns of the state: columns do not
+//                     depend on one another) walks the sequence's new tokens in order with its share of the
+//                     state in registers: thread (j, r) owns column j of the tile and the rows r, r + R,
 //                     r + 2R, ...; it reads the state from the slot's row before the first token and
 //                     writes it back after the last.  A decode step is the same kernel with one token.
 //                     The activation, the decay, the state and o are 32-bit whatever T.
@@ -22,20 +23,23 @@ namespace {
 
 __device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
 
+constexpr int COL_TILE = 64;      // columns of the state per block
+constexpr int MAX_THREADS = 512;
+
 template <typename T, int ROWS>
-__global__ void lightning_scan_kernel(const T* __restrict__ proj, float* __restrict__ state, const float* __restrict__ decay,
+__global__ void __launch_bounds__(MAX_THREADS) lightning_scan_kernel(const T* __restrict__ proj, float* __restrict__ state, const float* __restrict__ decay,
                                       const int* __restrict__ seq_start, const int* __restrict__ seq_slots,
-                                      float* __restrict__ out, int H, int d, int vd, int R) {
+                                      float* __restrict__ out, int H, int d, int vd, int R, int vt) {
     extern __shared__ float smem[];
     float* q_s = smem;                 // [d]
     float* k_s = q_s + d;              // [d]
-    float* v_s = k_s + d;              // [vd]
-    float* red = v_s + vd;             // [R][vd]
+    float* v_s = k_s + d;              // [vt]
+    float* red = v_s + vt;             // [R][vt]
     pdl_launch_dependents();
     pdl_wait();
-    const int head = blockIdx.x, seq = blockIdx.y;
-    const int tid = threadIdx.x, j = tid % vd, r = tid / vd;
-    const bool live = r < R;
+    const int head = blockIdx.x, seq = blockIdx.y, col0 = blockIdx.z * vt;
+    const int tid = threadIdx.x, jt = tid % vt, j = col0 + jt, r = tid / vt;
+    const bool live = r < R && j < vd;
     const float lam = decay[head];
     const int64_t cols = 2 * (int64_t)H * d + 2 * (int64_t)H * vd;
     float* S_g = state + ((int64_t)seq_slots[seq] * H + head) * d * vd;
@@ -51,10 +55,11 @@ __global__ void lightning_scan_kernel(const T* __restrict__ proj, float* __restr
             q_s[i] = silu_f32(to_f32<T>(row[(int64_t)head * d + i]));
             k_s[i] = silu_f32(to_f32<T>(row[(int64_t)(H + head) * d + i]));
         }
-        for (int i = tid; i < vd; i += blockDim.x) v_s[i] = silu_f32(to_f32<T>(row[2 * (int64_t)H * d + (int64_t)head * vd + i]));
+        for (int i = tid; i < vt; i += blockDim.x)
+            v_s[i] = col0 + i < vd ? silu_f32(to_f32<T>(row[2 * (int64_t)H * d + (int64_t)head * vd + col0 + i])) : 0.0f;
         __syncthreads();
         if (live) {
-            const float v = v_s[j];
+            const float v = v_s[jt];
             float part = 0.0f;
 #pragma unroll
             for (int n = 0; n < ROWS; ++n) {
@@ -64,13 +69,13 @@ __global__ void lightning_scan_kernel(const T* __restrict__ proj, float* __restr
                     part = fmaf(S[n], q_s[i], part);
                 }
             }
-            red[r * vd + j] = part;
+            red[r * vt + jt] = part;
         }
         __syncthreads();
-        if (tid < vd) {
+        if (tid < vt && col0 + tid < vd) {
             float o = 0.0f;
-            for (int rr = 0; rr < R; ++rr) o += red[rr * vd + tid];
-            out[((int64_t)t * H + head) * vd + tid] = o;
+            for (int rr = 0; rr < R; ++rr) o += red[rr * vt + tid];
+            out[((int64_t)t * H + head) * vd + col0 + tid] = o;
         }
     }
     if (live) {
@@ -87,49 +92,49 @@ int lightning_scan_launch(const T* proj, float* state, const float* decay, const
                           int n_seqs, int H, int d, int vd, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || d <= 0 || vd <= 0 || d > 256 || vd > 256 || n_seqs > 65535) return Q3_ERR_BAD_SIZE;
-    const int R = min(d, 1024 / vd);                   // row slices: as many as a block of 1024 threads holds
-    const int rows = (d + R - 1) / R;
-    const int threads = ((vd * R + 31) / 32) * 32;
-    const size_t smem = (size_t)(2 * d + vd + R * vd) * sizeof(float);
-    const dim3 grid(H, n_seqs);
+    const int vt = min(vd, COL_TILE);
+    const int R = min(d, MAX_THREADS / vt);            // row slices: as many as a block holds
+    const int rows = (d + R - 1) / R;                  // at most 32: d <= 256, R >= 8 unless d is smaller
+    const int threads = ((vt * R + 31) / 32) * 32;
+    const size_t smem = (size_t)(2 * d + vt + R * vt) * sizeof(float);
+    const dim3 grid(H, n_seqs, (vd + vt - 1) / vt);
 #define Q3_SCAN(ROWS)                                                                                                    \
     return (int)q3_launch(lightning_scan_kernel<T, ROWS>, grid, dim3(threads), smem, stream, proj, state, decay, seq_start, \
-                          seq_slots, out, H, d, vd, R)
+                          seq_slots, out, H, d, vd, R, vt)
     if (rows <= 1) Q3_SCAN(1);
     if (rows <= 2) Q3_SCAN(2);
     if (rows <= 4) Q3_SCAN(4);
     if (rows <= 8) Q3_SCAN(8);
     if (rows <= 16) Q3_SCAN(16);
-    if (rows <= 32) Q3_SCAN(32);
-    Q3_SCAN(64);
+    Q3_SCAN(32);
 #undef Q3_SCAN
 }
 
 // ---------------------------------------------------------------- prompts, a chunk of tokens at a time
-// One block of 256 threads per (head, sequence).  Per chunk of C tokens the block holds q, k (C x d), v (C x vd)
-// and the C x C matrix of decayed scores in shared memory and the state in registers as in the scan: thread
-// (j, r) owns column j and rows r, r + R, ...  All sums run in ascending order of their index.
+// One block per (head, sequence, tile of columns), as in the scan.  Per chunk of C tokens the block holds q, k
+// (C x d), its columns of v and the C x C matrix of decayed scores in shared memory and its share of the state in
+// registers: thread (j, r) owns column j and rows r, r + R, ...  All sums run in ascending order of their index.
 constexpr int CHUNK = 32;
 
 template <typename T, int ROWS>
-__global__ void lightning_chunks_kernel(const T* __restrict__ proj, float* __restrict__ state, const float* __restrict__ decay,
+__global__ void __launch_bounds__(MAX_THREADS) lightning_chunks_kernel(const T* __restrict__ proj, float* __restrict__ state, const float* __restrict__ decay,
                                         const int* __restrict__ seq_start, const int* __restrict__ seq_slots,
-                                        float* __restrict__ out, int H, int d, int vd, int R) {
+                                        float* __restrict__ out, int H, int d, int vd, int R, int vt) {
     extern __shared__ float smem[];
     float* q_s = smem;                         // [C][d + 1]
     float* k_s = q_s + CHUNK * (d + 1);        // [C][d + 1]
-    float* v_s = k_s + CHUNK * (d + 1);        // [C][vd]
-    float* a_s = v_s + CHUNK * vd;             // [C][C + 1]: decay^(i-j) (q_i . k_j), j <= i
-    float* red = a_s + CHUNK * (CHUNK + 1);    // [R][C][vd] partial S_0^T q_i
+    float* v_s = k_s + CHUNK * (d + 1);        // [C][vt]
+    float* a_s = v_s + CHUNK * vt;             // [C][C + 1]: decay^(i-j) (q_i . k_j), j <= i
+    float* red = a_s + CHUNK * (CHUNK + 1);    // [R][C][vt] partial S_0^T q_i
     __shared__ float pw[CHUNK + 1];            // decay^n
     pdl_launch_dependents();
     pdl_wait();
-    const int head = blockIdx.x, seq = blockIdx.y;
-    const int tid = threadIdx.x, nthreads = blockDim.x, j = tid % vd, r = tid / vd;
-    const bool live = r < R;
+    const int head = blockIdx.x, seq = blockIdx.y, col0 = blockIdx.z * vt;
+    const int tid = threadIdx.x, nthreads = blockDim.x, jt = tid % vt, j = col0 + jt, r = tid / vt;
+    const bool live = r < R && j < vd;
     const float lam = decay[head];
     const float l2 = lam > 0.0f ? log2f(lam) : 0.0f;
-    if (tid <= CHUNK) pw[tid] = tid == 0 ? 1.0f : (lam > 0.0f ? exp2f((float)tid * l2) : 0.0f);
+    for (int n = tid; n <= CHUNK; n += nthreads) pw[n] = n == 0 ? 1.0f : (lam > 0.0f ? exp2f((float)n * l2) : 0.0f);
     const int64_t cols = 2 * (int64_t)H * d + 2 * (int64_t)H * vd;
     const int dp = d + 1;
     float* S_g = state + ((int64_t)seq_slots[seq] * H + head) * d * vd;
@@ -149,9 +154,9 @@ __global__ void lightning_chunks_kernel(const T* __restrict__ proj, float* __res
             q_s[i * dp + c] = silu_f32(to_f32<T>(row[(int64_t)head * d + c]));
             k_s[i * dp + c] = silu_f32(to_f32<T>(row[(int64_t)(H + head) * d + c]));
         }
-        for (int x = tid; x < C * vd; x += nthreads) {
-            const int i = x / vd, c = x % vd;
-            v_s[x] = silu_f32(to_f32<T>(proj[(int64_t)(t0 + i) * cols + 2 * (int64_t)H * d + (int64_t)head * vd + c]));
+        for (int x = tid; x < C * vt; x += nthreads) {
+            const int i = x / vt, c = col0 + x % vt;
+            v_s[x] = c < vd ? silu_f32(to_f32<T>(proj[(int64_t)(t0 + i) * cols + 2 * (int64_t)H * d + (int64_t)head * vd + c])) : 0.0f;
         }
         __syncthreads();
         // scores inside the chunk
@@ -173,18 +178,19 @@ __global__ void lightning_chunks_kernel(const T* __restrict__ proj, float* __res
                     const int row = r + n * R;
                     if (row < d) part = fmaf(S[n], q_s[i * dp + row], part);
                 }
-                red[(r * CHUNK + i) * vd + j] = part;
+                red[(r * CHUNK + i) * vt + jt] = part;
             }
         }
         __syncthreads();
         // o_i = decay^(i+1) * (S_0^T q_i) + sum_j a_ij v_j
-        for (int x = tid; x < C * vd; x += nthreads) {
-            const int i = x / vd, c = x % vd;
+        for (int x = tid; x < C * vt; x += nthreads) {
+            const int i = x / vt, c = x % vt;
+            if (col0 + c >= vd) continue;
             float inter = 0.0f;
-            for (int rr = 0; rr < R; ++rr) inter += red[(rr * CHUNK + i) * vd + c];
+            for (int rr = 0; rr < R; ++rr) inter += red[(rr * CHUNK + i) * vt + c];
             float intra = 0.0f;
-            for (int jj = 0; jj <= i; ++jj) intra = fmaf(a_s[i * (CHUNK + 1) + jj], v_s[jj * vd + c], intra);
-            out[((int64_t)(t0 + i) * H + head) * vd + c] = fmaf(pw[i + 1], inter, intra);
+            for (int jj = 0; jj <= i; ++jj) intra = fmaf(a_s[i * (CHUNK + 1) + jj], v_s[jj * vt + c], intra);
+            out[((int64_t)(t0 + i) * H + head) * vd + col0 + c] = fmaf(pw[i + 1], inter, intra);
         }
         // the state after the chunk
         if (live) {
@@ -193,7 +199,7 @@ __global__ void lightning_chunks_kernel(const T* __restrict__ proj, float* __res
                 const int row = r + n * R;
                 if (row < d) {
                     float add = 0.0f;
-                    for (int jj = 0; jj < C; ++jj) add = fmaf(pw[C - 1 - jj] * k_s[jj * dp + row], v_s[jj * vd + j], add);
+                    for (int jj = 0; jj < C; ++jj) add = fmaf(pw[C - 1 - jj] * k_s[jj * dp + row], v_s[jj * vt + jt], add);
                     S[n] = fmaf(pw[C], S[n], add);
                 }
             }
@@ -213,13 +219,14 @@ int lightning_chunks_launch(const T* proj, float* state, const float* decay, con
                             float* out, int n_seqs, int H, int d, int vd, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || d <= 0 || vd <= 0 || d > 256 || vd > 256 || n_seqs > 65535) return Q3_ERR_BAD_SIZE;
-    const int R = min(d, 1024 / vd);
+    const int vt = min(vd, COL_TILE);
+    const int R = min(d, MAX_THREADS / vt);
     const int rows = (d + R - 1) / R;
-    const int threads = ((vd * R + 31) / 32) * 32;
-    const size_t smem = (size_t)(2 * CHUNK * (d + 1) + CHUNK * vd + CHUNK * (CHUNK + 1) + R * CHUNK * vd) * sizeof(float);
+    const int threads = ((vt * R + 31) / 32) * 32;
+    const size_t smem = (size_t)(2 * CHUNK * (d + 1) + CHUNK * vt + CHUNK * (CHUNK + 1) + R * CHUNK * vt) * sizeof(float);
     if (smem > 200 * 1024) return Q3_ERR_BAD_SIZE;
-    const dim3 grid(H, n_seqs);
-    static Q3PerDevice allowed[7];
+    const dim3 grid(H, n_seqs, (vd + vt - 1) / vt);
+    static Q3PerDevice allowed[6];
 #define Q3_CHUNKS(ROWS, SLOT)                                                                                             \
     {                                                                                                                     \
         if (smem > 48 * 1024) {                                                                                           \
@@ -227,15 +234,14 @@ int lightning_chunks_launch(const T* proj, float* state, const float* decay, con
             if (e != cudaSuccess) return (int)e;                                                                          \
         }                                                                                                                 \
         return (int)q3_launch(lightning_chunks_kernel<T, ROWS>, grid, dim3(threads), smem, stream, proj, state, decay,     \
-                              seq_start, seq_slots, out, H, d, vd, R);                                                    \
+                              seq_start, seq_slots, out, H, d, vd, R, vt);                                                \
     }
     if (rows <= 1) Q3_CHUNKS(1, 0)
     if (rows <= 2) Q3_CHUNKS(2, 1)
     if (rows <= 4) Q3_CHUNKS(4, 2)
     if (rows <= 8) Q3_CHUNKS(8, 3)
     if (rows <= 16) Q3_CHUNKS(16, 4)
-    if (rows <= 32) Q3_CHUNKS(32, 5)
-    Q3_CHUNKS(64, 6)
+    Q3_CHUNKS(32, 5)
 #undef Q3_CHUNKS
 }
 

@@ -495,8 +495,9 @@ def lightning_attention(proj: torch.Tensor, state: torch.Tensor, decay: torch.Te
 
 def lightning_chunks_fit(d: int, vd: int) -> bool:
     """Whether the chunked form's buffers fit in an SM's shared memory for these head sizes."""
-    R = min(d, 1024 // vd)
-    return (2 * 32 * (d + 1) + 32 * vd + 32 * 33 + R * 32 * vd) * 4 <= 200 * 1024
+    vt = min(vd, 64)
+    R = min(d, 512 // vt)
+    return (2 * 32 * (d + 1) + 32 * vt + 32 * 33 + R * 32 * vt) * 4 <= 200 * 1024
 
 
 def gated_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:

@@ -118,13 +118,22 @@ def lively_weights(specs, seed):
     return out
 
 
-def make_folder(tmp_path, cfg, seed, name="model", tensors=None):
-    """Write a model folder; returns (folder, weights as float64 NumPy arrays by name)."""
+def make_folder(tmp_path, cfg, seed, name="model", tensors=None, decided=False):
+    """Write a model folder; returns (folder, weights as float64 NumPy arrays by name).  `decided`: the routers'
+    corrections lie 2 apart (scores lie in [0, 1]), so the SET of chosen experts is the same for every token and no
+    rounding can change it, while the weights still follow the token: what a comparison in bfloat16 needs, where a
+    close call between two experts would otherwise be decided differently by a rounded input."""
     import torch
     import qwen3_b200 as q
     config = q.config_from_dict(cfg)
     if tensors is None:
         tensors = lively_weights(q.build_model(config.plan()).weight_specs(), seed)
+    if decided:
+        gen = torch.Generator().manual_seed(seed + 1)
+        for key in tensors:
+            if key.endswith(".correction"):
+                n = tensors[key].numel()
+                tensors[key] = (2.0 * torch.randperm(n, generator=gen).float() - n).to(torch.bfloat16)
     folder = os.path.join(str(tmp_path), name)
     q.write_model_folder(folder, config, tensors)
     return folder, {k: v.to(torch.float64).numpy() for k, v in tensors.items()}
