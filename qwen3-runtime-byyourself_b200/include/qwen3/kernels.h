@@ -46,6 +46,9 @@ int q3_silu_mul_bf16(const void* gate_up, void* out, int64_t rows, int inter, in
 /* the same with the activation as a parameter: act 0 = SiLU, 1 = the tanh form of GELU */
 int q3_act_mul_f32(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, int act, void* stream);
 int q3_act_mul_bf16(const void* gate_up, void* out, int64_t rows, int inter, int interleaved, int act, void* stream);
+/* out = act(x) elementwise: act 0 = SiLU, 1 = the tanh form of GELU, 2 = GELU with the error function */
+int q3_activation_f32(const void* x, void* out, int64_t n, int act, void* stream);
+int q3_activation_bf16(const void* x, void* out, int64_t n, int act, void* stream);
 /* out[r] = x[idx[r]] (+ delta[idx[r]]) */
 int q3_gather_rows_f32(const void* x, const void* delta, const int* idx, void* out, int64_t rows, int size, void* stream);
 int q3_gather_rows_bf16(const void* x, const void* delta, const int* idx, void* out, int64_t rows, int size, void* stream);
@@ -80,20 +83,24 @@ int q3_scale_softcap_f32(float* x, int64_t n, float scale, float cap, void* stre
 int q3_qkv_prepare_f32(const void* qkv, void* q_out, void* k_pages, void* v_pages, const float* q_norm_w, const float* k_norm_w,
                        const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos, const int* page_table,
                        int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim,
-                       const float* bias, int value_dim, void* stream);
+                       const float* bias, int value_dim, int value_heads, void* stream);
 int q3_qkv_prepare_bf16(const void* qkv, void* q_out, void* k_pages, void* v_pages, const float* q_norm_w, const float* k_norm_w,
                         const float* cos_tab, const float* sin_tab, const int* token_seq, const int* token_pos, const int* page_table,
                         int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d, float eps, int write_kv, int rotary_dim,
-                       const float* bias, int value_dim, void* stream);
-/* causal grouped-query attention of every token over its sequence's pages; window 0 = every key; value_dim 0 = d;
+                       const float* bias, int value_dim, int value_heads, void* stream);
+/* (q3_qkv_prepare: value_heads 0 = nkv; fewer value heads than key heads: values that several key heads share)
+   causal grouped-query attention of every token over its sequence's pages; window 0 = every key; value_dim 0 = d;
+   value_heads 0 = nkv, else each value head serves nkv / value_heads key heads; out_f32: `out` is float whatever q is;
    softcap > 0: scores s <- softcap * tanh(s / softcap); chunk > 0: a query reads the keys of its own chunk of that many
    positions only; sink != 0: one more term exp(0) in the softmax's denominator */
 int q3_attention_generic_f32(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                              const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
-                             float scale, int window, int value_dim, float softcap, int chunk, int sink, void* stream);
+                             float scale, int window, int value_dim, float softcap, int chunk, int sink, int value_heads, int out_f32,
+                             void* stream);
 int q3_attention_generic_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_seq,
                               const int* token_pos, const int* page_table, int pages_per_seq, int64_t n_tokens, int nq, int nkv, int d,
-                              float scale, int window, int value_dim, float softcap, int chunk, int sink, void* stream);
+                              float scale, int window, int value_dim, float softcap, int chunk, int sink, int value_heads, int out_f32,
+                             void* stream);
 
 /* the same from the q/k/v projection's output as it is: bias (may be null), rotation of the first rotary_dim values of q and k
    (tables may be null) and the write of the new key and value into their pages in the attention's own kernel */
@@ -177,6 +184,68 @@ int q3_gemm_tcgen05_pair_qkv_bf16(const void* X, const void* W, int M, int K, vo
 int q3_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int out_is_f32, int gated, int splits,
                               int* status, void* stream);
 int q3_gemm_tcgen05_pair_capacity(int splits);
+
+/* ---- hyper.cu: a hidden state of several streams per token, float32 [token, streams, hidden] ------------------ */
+/* out[t] = `copies` times table[ids[t]] * scale side by side */
+int q3_embedding_streams_f32(const int* ids, const void* table, float* out, int64_t n_tokens, int hidden, int vocab, float scale,
+                             int copies, void* stream);
+int q3_embedding_streams_bf16(const int* ids, const void* table, float* out, int64_t n_tokens, int hidden, int vocab, float scale,
+                              int copies, void* stream);
+/* one pass: settle a pending sublayer output (x_to <- sum_from mix[from][to] x_from + out_coef[to] branch; branch may be
+   null), u = sum_s in_coef[s] x_s (null: ones), out = u / sqrt(mean(u^2) + eps) * norm_w (normalize 0: u itself; out may be
+   null).  rows != null: only those tokens, one output row each, the streams are not written */
+int q3_hyper_norm_f32(float* streams, const void* branch, const float* mix, const float* out_coef, const float* in_coef,
+                      const float* norm_w, float eps, void* out, int out_f32, const int* rows, int64_t n_rows, int n_streams,
+                      int hidden, int normalize, void* stream);
+int q3_hyper_norm_bf16(float* streams, const void* branch, const float* mix, const float* out_coef, const float* in_coef,
+                       const float* norm_w, float eps, void* out, int out_f32, const int* rows, int64_t n_rows, int n_streams,
+                       int hidden, int normalize, void* stream);
+
+/* ---- lightning.cu: linear attention with a per-head decay and a float32 state [slot, heads, d, vd] ------------- */
+/* proj [N, 2 heads d + 2 heads vd] = q, k, v (SiLU applied here), gate; S <- decay S + k v^T, out = S^T q, token by token */
+int q3_lightning_scan_f32(const void* proj, float* state, const float* decay, const int* seq_start, const int* seq_slots,
+                          float* out, int n_seqs, int heads, int d, int vd, void* stream);
+int q3_lightning_scan_bf16(const void* proj, float* state, const float* decay, const int* seq_start, const int* seq_slots,
+                           float* out, int n_seqs, int heads, int d, int vd, void* stream);
+/* the same for prompts, 32 tokens at a time */
+int q3_lightning_chunks_f32(const void* proj, float* state, const float* decay, const int* seq_start, const int* seq_slots,
+                            float* out, int n_seqs, int heads, int d, int vd, void* stream);
+int q3_lightning_chunks_bf16(const void* proj, float* state, const float* decay, const int* seq_start, const int* seq_slots,
+                             float* out, int n_seqs, int heads, int d, int vd, void* stream);
+/* out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate), row by row; gate rows are gate_stride apart */
+int q3_gated_norm_f32(const float* o, const void* gate, int64_t gate_stride, const float* w, float eps, void* out,
+                      int64_t n_tokens, int size, void* stream);
+int q3_gated_norm_bf16(const float* o, const void* gate, int64_t gate_stride, const float* w, float eps, void* out,
+                       int64_t n_tokens, int size, void* stream);
+
+/* ---- differential.cu ---------------------------------------------------------------------------------------- */
+/* a float32 [token, group, 2 maps, per_group, vd]; out[t, h] = unit_rms(a1 - lambda a2) * gain */
+int q3_diff_combine_f32(const float* a, void* out, int64_t n_tokens, int heads, int per_group, int vd, float lambda, float eps,
+                        float gain, void* stream);
+int q3_diff_combine_bf16(const float* a, void* out, int64_t n_tokens, int heads, int per_group, int vd, float lambda, float eps,
+                         float gain, void* stream);
+
+/* ---- moe.cu: a routed feed-forward ---------------------------------------------------------------------------- */
+/* per token: float32 router logits, softmax, choice by score + correction within the kept groups, weights = scores;
+   the outputs from n_real on are identity experts (their weights are summed into id_weight) */
+int q3_moe_route_f32(const void* h, const void* w_router, const float* correction, int* top_ids, float* top_w, float* id_weight,
+                     int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, void* stream);
+int q3_moe_route_bf16(const void* h, const void* w_router, const float* correction, int* top_ids, float* top_w, float* id_weight,
+                      int64_t n_tokens, int hidden, int n_out, int n_real, int top, int group_count, int group_keep, void* stream);
+/* offsets [n_real + 1], slot_of_pair (-1: identity) and pair_of_slot of the (token, choice) pairs laid out by expert */
+int q3_moe_sort(const int* top_ids, int n_pairs, int n_real, int* offsets, int* slot_of_pair, int* pair_of_slot, void* stream);
+/* act[slot] = g sigmoid(alpha g) (u + 1), g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit); y[slot] = W_down act */
+int q3_moe_experts_f32(const void* h, const void* w_gate_up, const void* w_down, const int* offsets, const int* pair_of_slot,
+                       void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha,
+                       void* stream);
+int q3_moe_experts_bf16(const void* h, const void* w_gate_up, const void* w_down, const int* offsets, const int* pair_of_slot,
+                        void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha,
+                        void* stream);
+/* out[t] = sum_k top_w[t, k] y[slot_of_pair[t, k]] + id_weight[t] h[t] */
+int q3_moe_combine_f32(const float* y, const void* h, const int* slot_of_pair, const float* top_w, const float* id_weight,
+                       void* out, int64_t n_tokens, int top, int hidden, void* stream);
+int q3_moe_combine_bf16(const float* y, const void* h, const int* slot_of_pair, const float* top_w, const float* id_weight,
+                        void* out, int64_t n_tokens, int top, int hidden, void* stream);
 
 /* ---- sampling.cu ------------------------------------------------------------------------------------------ */
 /* out[r] = index of the highest logit among the first `valid` (lowest id among equals, NaN as -inf) */
