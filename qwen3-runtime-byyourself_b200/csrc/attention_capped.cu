@@ -87,7 +87,19 @@ __device__ __forceinline__ float score_log2(float dot, float scale, float cap, f
     return v * LOG2E;
 }
 
-__device__ __forceinline__ int chunk_start(int pos, int chunk) { return chunk > 0 ? pos / chunk * chunk : 0; }
+// The first key position `pos` sees.  `chunk` > 0: the start of its chunk; `chunk` < 0 stands for a sliding window of
+// -chunk keys (itself and the -chunk - 1 before it); 0: every key.  It never decreases with `pos`.
+__device__ __forceinline__ int chunk_start(int pos, int chunk) {
+    return chunk > 0 ? pos / chunk * chunk : (chunk < 0 ? max(pos + chunk + 1, 0) : 0);
+}
+
+template <typename TO> __device__ __forceinline__ void store_pair(TO* p, float a, float b);
+template <> __device__ __forceinline__ void store_pair<bf16>(bf16* p, float a, float b) {
+    *reinterpret_cast<uint32_t*>(p) = pack_bf16(a, b);
+}
+template <> __device__ __forceinline__ void store_pair<float>(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
 
 template <int ROWS, int COLS, int ROW_BYTES, int THREADS>
 __device__ __forceinline__ void load_rows(uint32_t dst, const bf16* src, int tid) {
@@ -104,18 +116,19 @@ constexpr int BM = 64;
 constexpr int K_TILE = PAGE * K_ROW, V_TILE = PAGE * V_ROW;
 constexpr int PREFILL_SMEM = 2 * (K_TILE + V_TILE);
 
+template <typename TO>
 __global__ void __launch_bounds__(WARPS * 32)
 prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
-                      bf16* __restrict__ out, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
+                      TO* __restrict__ out, const int* __restrict__ seq_start, const int* __restrict__ seq_pos0,
                       const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, float scale, float cap, int chunk,
-                      int sink) {
+                      int sink, int nv) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
     const int tile = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
     const int t0 = seq_start[seq], n_new = seq_start[seq + 1] - t0;
     if (tile * BM >= n_new) return;
-    const int kvh = head / (nq / nkv);
+    const int kvh = head / (nq / nkv), vh = kvh / (nkv / nv);      // nv value heads, each shared by nkv / nv key heads
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, tq = lane & 3;
     const int pos0 = seq_pos0[seq];
     const int* pages = page_table + (int64_t)seq * pages_per_seq;
@@ -154,10 +167,10 @@ prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pag
 
     auto issue = [&](int pg) {
         if (pg < pg_end) {
-            const int64_t tile_at = ((int64_t)pages[pg] * nkv + kvh) * PAGE;
+            const int64_t k_at = ((int64_t)pages[pg] * nkv + kvh) * PAGE, v_at = ((int64_t)pages[pg] * nv + vh) * PAGE;
             const uint32_t dst = base + ((pg - pg_begin) & 1) * (K_TILE + V_TILE);
-            load_rows<PAGE, D, K_ROW, WARPS * 32>(dst, k_pages + tile_at * D, threadIdx.x);
-            load_rows<PAGE, VD, V_ROW, WARPS * 32>(dst + K_TILE, v_pages + tile_at * VD, threadIdx.x);
+            load_rows<PAGE, D, K_ROW, WARPS * 32>(dst, k_pages + k_at * D, threadIdx.x);
+            load_rows<PAGE, VD, V_ROW, WARPS * 32>(dst + K_TILE, v_pages + v_at * VD, threadIdx.x);
         }
         cp_async_commit();
     };
@@ -250,13 +263,13 @@ prefill_capped_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pag
     cp_async_wait<0>();
 
     const float inv_lo = 1.0f / l_run[0], inv_hi = 1.0f / l_run[1];
-    bf16* o_lo = out + ((int64_t)(t0 + r_lo) * nq + head) * VD;
-    bf16* o_hi = out + ((int64_t)(t0 + r_hi) * nq + head) * VD;
+    TO* o_lo = out + ((int64_t)(t0 + r_lo) * nq + head) * VD;
+    TO* o_hi = out + ((int64_t)(t0 + r_hi) * nq + head) * VD;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
         const int c = n * 8 + tq * 2;
-        if (ok_lo) *reinterpret_cast<uint32_t*>(o_lo + c) = pack_bf16(o[n][0] * inv_lo, o[n][1] * inv_lo);
-        if (ok_hi) *reinterpret_cast<uint32_t*>(o_hi + c) = pack_bf16(o[n][2] * inv_hi, o[n][3] * inv_hi);
+        if (ok_lo) store_pair<TO>(o_lo + c, o[n][0] * inv_lo, o[n][1] * inv_lo);
+        if (ok_hi) store_pair<TO>(o_hi + c, o[n][2] * inv_hi, o[n][3] * inv_hi);
     }
 }
 
@@ -313,7 +326,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, const bf16* v_pages,
                            float* __restrict__ part, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                            const int* __restrict__ page_table, int pages_per_seq, int nq, int nkv, float scale, float cap,
-                           int chunk, const FusedArgs fused) {
+                           int chunk, const FusedArgs fused, int nv) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -334,9 +347,10 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, cons
     auto issue = [&](int i) {
         if (i < count) {
             const int64_t at = ((int64_t)pages[pg_begin + i] * nkv + kvh) * PAGE + warp * KEYS_PER_WARP;
+            const int64_t v_at = ((int64_t)pages[pg_begin + i] * nv + kvh / (nkv / nv)) * PAGE + warp * KEYS_PER_WARP;
             const uint32_t dst = pipe + (i % STAGES) * (K_PANEL + V_PANEL);
             load_rows<KEYS_PER_WARP, D, K_ROW, 32>(dst, k_pages + at * D, lane);
-            load_rows<KEYS_PER_WARP, VD, V_ROW, 32>(dst + K_PANEL, v_pages + at * VD, lane);
+            load_rows<KEYS_PER_WARP, VD, V_ROW, 32>(dst + K_PANEL, v_pages + v_at * VD, lane);
         }
         cp_async_commit();
     };
@@ -521,7 +535,8 @@ decode_capped_split_kernel(const bf16* __restrict__ q, const bf16* k_pages, cons
 }
 
 // One block per (query head, token): the splits' partial results, the sink, the division.
-__global__ void decode_capped_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, int nq, int n_splits, int sink) {
+template <typename TO>
+__global__ void decode_capped_merge_kernel(const float* __restrict__ part, TO* __restrict__ out, int nq, int n_splits, int sink) {
     pdl_launch_dependents();
     pdl_wait();
     const int head = blockIdx.x;
@@ -541,7 +556,7 @@ __global__ void decode_capped_merge_kernel(const float* __restrict__ part, bf16*
             const float ms = p[s * (VD + 2) + VD];
             if (ms != -INFINITY) acc += exp2f(ms - m) * p[s * (VD + 2) + c];
         }
-        out[(t * nq + head) * VD + c] = __float2bfloat16_rn(acc * inv);
+        out[(t * nq + head) * VD + c] = from_f32<TO>(acc * inv);
     }
 }
 
@@ -554,28 +569,43 @@ Q3_EXPORT int q3_attention_capped_value_dim() { return VD; }
 Q3_EXPORT int q3_attention_capped_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, void* out,
                                                const int* seq_start, const int* seq_pos0, const int* page_table,
                                                int pages_per_seq, int n_seqs, int max_new, int nq, int nkv, float scale,
-                                               float softcap, int chunk, int sink, void* stream) {
+                                               float softcap, int chunk, int sink, int window, int value_heads, int out_f32,
+                                               void* stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || softcap < 0.0f || chunk < 0) return Q3_ERR_BAD_SIZE;
+    if (value_heads <= 0) value_heads = nkv;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nkv % value_heads != 0 || softcap < 0.0f || chunk < 0 || window < 0 ||
+        (chunk > 0 && window > 0))
+        return Q3_ERR_BAD_SIZE;
     if (n_seqs > 65535 || nq > 65535) return Q3_ERR_TOO_LARGE;
-    static Q3PerDevice configured;
-    {
-        cudaError_t e = q3_allow_shared_memory(prefill_capped_kernel, PREFILL_SMEM, configured);
-        if (e != cudaSuccess) return (int)e;
-    }
+    const int span = window > 0 ? -window : chunk;             // see chunk_start
+    static Q3PerDevice configured[2];
     const dim3 grid((max_new + BM - 1) / BM, nq, n_seqs);
-    return (int)q3_launch(prefill_capped_kernel, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream, (const bf16*)q,
+    if (out_f32) {
+        cudaError_t e = q3_allow_shared_memory(prefill_capped_kernel<float>, PREFILL_SMEM, configured[1]);
+        if (e != cudaSuccess) return (int)e;
+        return (int)q3_launch(prefill_capped_kernel<float>, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream, (const bf16*)q,
+                              (const bf16*)k_pages, (const bf16*)v_pages, (float*)out, seq_start, seq_pos0, page_table,
+                              pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads);
+    }
+    cudaError_t e = q3_allow_shared_memory(prefill_capped_kernel<bf16>, PREFILL_SMEM, configured[0]);
+    if (e != cudaSuccess) return (int)e;
+    return (int)q3_launch(prefill_capped_kernel<bf16>, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream, (const bf16*)q,
                           (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, seq_start, seq_pos0, page_table,
-                          pages_per_seq, nq, nkv, scale, softcap, chunk, sink);
+                          pages_per_seq, nq, nkv, scale, softcap, span, sink, value_heads);
 }
 
 // One new token per sequence: scratch holds n_tokens * nq * n_splits * (VD + 2) float32.
 Q3_EXPORT int q3_attention_capped_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
                                               const int* token_seq, const int* token_pos, const int* page_table,
                                               int pages_per_seq, int64_t n_tokens, int nq, int nkv, float scale, float softcap,
-                                              int chunk, int sink, int n_splits, void* stream) {
+                                              int chunk, int sink, int n_splits, int window, int value_heads, int out_f32,
+                                              void* stream) {
     if (n_tokens <= 0) return 0;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || softcap < 0.0f || chunk < 0 || n_splits <= 0) return Q3_ERR_BAD_SIZE;
+    if (value_heads <= 0) value_heads = nkv;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || nkv % value_heads != 0 || softcap < 0.0f || chunk < 0 ||
+        window < 0 || (chunk > 0 && window > 0) || n_splits <= 0)
+        return Q3_ERR_BAD_SIZE;
+    const int span = window > 0 ? -window : chunk;             // see chunk_start
     if (n_tokens > 65535 || nkv > 65535 || nq > 0x7fffffff / 2) return Q3_ERR_TOO_LARGE;
     static Q3PerDevice configured;
     {
@@ -585,9 +615,12 @@ Q3_EXPORT int q3_attention_capped_decode_bf16(const void* q, const void* k_pages
     FusedArgs none = {};
     cudaError_t e = q3_launch(decode_capped_split_kernel<false>, dim3(n_splits, nkv, (unsigned)n_tokens), dim3(WARPS * 32), DECODE_SMEM,
                               (cudaStream_t)stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, scratch, token_seq,
-                              token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, none);
+                              token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, span, none, value_heads);
     if (e != cudaSuccess) return (int)e;
-    return (int)q3_launch(decode_capped_merge_kernel, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
+    if (out_f32)
+        return (int)q3_launch(decode_capped_merge_kernel<float>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
+                              (cudaStream_t)stream, (const float*)scratch, (float*)out, nq, n_splits, sink);
+    return (int)q3_launch(decode_capped_merge_kernel<bf16>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
                           (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink);
 }
 
@@ -613,8 +646,8 @@ Q3_EXPORT int q3_attention_capped_decode_fused_bf16(const void* qkv, void* k_pag
     fused.rot = rotary_dim > 0 ? rotary_dim : D;
     cudaError_t e = q3_launch(decode_capped_split_kernel<true>, dim3(n_splits, nkv, (unsigned)n_tokens), dim3(WARPS * 32),
                               DECODE_SMEM_FUSED, (cudaStream_t)stream, (const bf16*)nullptr, (const bf16*)k_pages, (const bf16*)v_pages,
-                              scratch, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, fused);
+                              scratch, token_seq, token_pos, page_table, pages_per_seq, nq, nkv, scale, softcap, chunk, fused, nkv);
     if (e != cudaSuccess) return (int)e;
-    return (int)q3_launch(decode_capped_merge_kernel, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
+    return (int)q3_launch(decode_capped_merge_kernel<bf16>, dim3(nq, (unsigned)n_tokens), dim3(VD >= 128 ? 128 : 64), 0,
                           (cudaStream_t)stream, (const float*)scratch, (bf16*)out, nq, n_splits, sink);
 }

@@ -39,10 +39,6 @@ FUSED_DECODE_KERNELS = []
 # Kernels that do the q/k/v product of a prompt step themselves, with norm, rotation and cache write in its
 # epilogue: fn(part, x, cache, q, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool (q is filled, the pages written)
 FUSED_PROJECTION_KERNELS = []
-# Kernels for parts that only the general kernel serves otherwise (`general_only`): they take the projection output
-# as it is and do the per-head norms, the cache write and the attention of any step themselves:
-# fn(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps) -> bool
-RAW_KERNELS = []
 
 
 TENSOR_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
@@ -68,12 +64,12 @@ class GQAAttention(Part):
         self.scale, self.window, self.prefix = float(scale), window, prefix
         self.value_dim, self.has_bias, self.sink = value_dim, bool(bias), bool(sink)
         # values that several key heads share (`value_heads` < num_kv_heads), and an output that stays in 32-bit for
-        # a part that goes on with it (`out_float32`): both are served by the general kernel only
+        # a part that goes on with it (`out_float32`): the general kernel and the `capped` tensor-core kernels take both
         self.value_heads = int(value_heads or num_kv_heads)
         if num_kv_heads % self.value_heads:
             raise ValueError("num_kv_heads must be a multiple of value_heads")
         self.out_float32 = bool(out_float32)
-        self.general_only = self.value_heads != num_kv_heads or self.out_float32
+        self.shared_values = self.value_heads != num_kv_heads or self.out_float32
         self.softcap = float(softcap) if softcap else 0.0
         self.chunk = int(chunk) if chunk else None
         self.names = dict(TENSOR_NAMES, **(names or {}))
@@ -84,7 +80,7 @@ class GQAAttention(Part):
         self.reordered = False       # the rows of the q and k projections follow the position encoding's kernel order
         # what the kernels written for Qwen3's attention take
         self.plain = not (self.has_bias or self.softcap or self.chunk or self.sink or value_dim != head_dim or head_dim % 16
-                          or self.general_only)
+                          or self.shared_values)
 
     # -- weights
     def weight_specs(self, prefix: str) -> dict:
@@ -157,7 +153,7 @@ class GQAAttention(Part):
         if tables and self.position is not None:
             self.position.prepare(ctx.max_positions, ctx.device)
             cos, sin = self.position.cos, self.position.sin
-        special = ctx.dtype == torch.bfloat16 and not self.general_only
+        special = ctx.dtype == torch.bfloat16
         if tables and not ctx.is_decode and special:
             q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
             for kernel in FUSED_PROJECTION_KERNELS:
@@ -170,10 +166,6 @@ class GQAAttention(Part):
             for kernel in FUSED_DECODE_KERNELS:
                 if kernel(self, qkv, cache, attn, ctx, table, qw, kw, norm_eps, cos, sin):
                     return attn
-        if tables and ctx.dtype == torch.bfloat16:
-            for kernel in RAW_KERNELS:                    # kernels of parts that take the projection output as it is
-                if kernel(self, qkv, cache, attn, ctx, table, qw, kw, norm_eps):
-                    return attn
         q = ctx.scratch.get("attn.q", (N, nq * d), ctx.dtype)
         if tables:
             ops.qkv_prepare(qkv, q, cache.keys, cache.values, qw, kw, cos, sin, ctx.token_seq, ctx.token_pos, table,
@@ -185,7 +177,7 @@ class GQAAttention(Part):
         return attn
 
     def attend(self, q, cache, out, ctx, table) -> None:
-        if ctx.dtype == torch.bfloat16 and not self.general_only:
+        if ctx.dtype == torch.bfloat16:
             for kernel in (DECODE_KERNELS if ctx.is_decode else PREFILL_KERNELS):
                 if kernel(self, q, cache, out, ctx, table):
                     return
@@ -311,14 +303,14 @@ def _prefill_capped_kernel(part, q, cache, out, ctx, table) -> bool:
         return False
     ops.attention_capped_prefill(q, cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table, ctx.n_seqs, ctx.max_new,
                                  part.num_heads, part.num_kv_heads, part.head_dim, part.value_dim, part.scale, part.softcap,
-                                 part.chunk, part.sink)
+                                 part.chunk, part.sink, window=part.window, value_heads=part.value_heads)
     return True
 
 
 def _prefill_capped_tcgen05_kernel(part, q, cache, out, ctx, table) -> bool:
     """The same on tcgen05 with TMA-fed tiles: head sizes 64 and 128, values as wide as keys, and enough new tokens
     for 128-row tiles to be worth it."""
-    if part.plain or not ops.attention_capped_prefill_tc_fits(part.head_dim, part.value_dim, part.window) \
+    if part.plain or part.shared_values or not ops.attention_capped_prefill_tc_fits(part.head_dim, part.value_dim, part.window) \
             or ctx.max_new < tc_prefill_rows or part.scale <= 0:
         return False
     ops.attention_capped_prefill_tc(q[:ctx.n_tokens], cache.keys, cache.values, out, ctx.seq_start, ctx.seq_pos0, table,
@@ -332,17 +324,19 @@ def _decode_capped_kernel(part, q, cache, out, ctx, table) -> bool:
     nq, nkv = part.num_heads, part.num_kv_heads
     if part.plain or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
         return False
-    splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device), part.chunk or ctx.max_context)
+    splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device),
+                                         min(part.chunk or part.window or ctx.max_context, ctx.max_context))
     scratch = ctx.scratch.get("attn.capped_scratch", (ctx.n_tokens * nq * splits * (part.value_dim + 2),), torch.float32)
     ops.attention_capped_decode(q, cache.keys, cache.values, out, scratch, ctx.token_seq, ctx.token_pos, table, ctx.n_tokens,
-                                nq, nkv, part.head_dim, part.value_dim, part.scale, part.softcap, part.chunk, part.sink, splits)
+                                nq, nkv, part.head_dim, part.value_dim, part.scale, part.softcap, part.chunk, part.sink, splits,
+                                window=part.window, value_heads=part.value_heads)
     return True
 
 
 def _decode_capped_fused_kernel(part, qkv, cache, out, ctx, table, q_norm_w, k_norm_w, eps, cos, sin) -> bool:
     """Bias, rotation, cache write and the split-key attention of a decode step in one kernel (and the small merge)."""
     nq, nkv = part.num_heads, part.num_kv_heads
-    if part.plain or q_norm_w is not None or cache.shared \
+    if part.plain or part.shared_values or part.window or q_norm_w is not None or cache.shared \
             or not ops.attention_capped_fits(part.head_dim, part.value_dim, part.window, nq // nkv):
         return False
     splits = ops.attention_capped_splits(ctx.n_tokens, nkv, _sm_count(ctx.device), part.chunk or ctx.max_context)

@@ -175,7 +175,8 @@ class Paged:
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,nv,d,vd,window", [(8, 2, 1, 16, 8, 70), (4, 4, 2, 24, 40, 64), (6, 2, 2, 32, 32, 0), (4, 2, 1, 48, 96, 136),
-                                                   (2, 2, 1, 11, 7, 1)])
+                                                   (2, 2, 1, 11, 7, 1), (16, 4, 2, 64, 128, 200), (8, 2, 1, 16, 16, 70), (4, 4, 4, 32, 16, 1),
+                                                   (2, 2, 2, 64, 64, 64)])
 def test_windowed_attention_with_shared_values_and_keys_that_stand_out(dtype, nq, nkv, nv, d, vd, window):
     """Every query is made to point at ONE earlier key whose score then dominates: keys just inside and just outside the
     window, at page borders, the first tokens, and far back.  Inside, the output is that key's value; outside, it is not.
@@ -226,6 +227,48 @@ def test_windowed_attention_with_shared_values_and_keys_that_stand_out(dtype, nq
                                                   block[:, (nq + nkv) * d + vh * vd:(nq + nkv) * d + (vh + 1) * vd], scale, window or None)
             worst = max(worst, float(np.abs(got[start[s]:start[s + 1], h] - want).max()))
     assert worst <= (2e-5 if dtype == "float32" else 3e-2), worst
+    wants = {}
+    for s_, n in enumerate(lengths):
+        block = rd[start[s_]:start[s_ + 1]]
+        for h in range(nq):
+            kh = h // (nq // nkv)
+            vh = kh // (nkv // nv)
+            wants[s_, h] = plain.window_softmax_attention(block[:, h * d:(h + 1) * d], block[:, (nq + kh) * d:(nq + kh + 1) * d],
+                                                          block[:, (nq + nkv) * d + vh * vd:(nq + nkv) * d + (vh + 1) * vd], scale, window or None)
+    if dtype == "bfloat16" and ops.attention_capped_fits(d, vd, window, nq // nkv):
+        # the tiled tensor-core kernels: whole prompts, prompts continued from a cached prefix, and single tokens
+        seq_start = dev(start, torch.int32)
+        zeros = dev(np.zeros(len(lengths)), torch.int32)
+        tiled = torch.full((N, nq * vd), 5.0, dtype=torch.float32, device="cuda")
+        ops.attention_capped_prefill(paged.q, paged.k_pages, paged.v_pages, tiled, seq_start, zeros, paged.table, len(lengths),
+                                     max(lengths), nq, nkv, d, vd, scale, window=window or None, value_heads=nv)
+        got_t = tiled.double().cpu().numpy().reshape(N, nq, vd)
+        for (s_, h), want in wants.items():
+            assert float(np.abs(got_t[start[s_]:start[s_ + 1], h] - want).max()) <= 3e-2, ("prompt", s_, h)
+        cut = [170, 64, 0, 1]                                   # tokens cached before the step
+        keep = np.concatenate([np.arange(start[i] + cut[i], start[i + 1]) for i in range(len(lengths))])
+        new_start = np.concatenate([[0], np.cumsum([lengths[i] - cut[i] for i in range(len(lengths))])])
+        part = torch.full((len(keep), nq * vd), 5.0, dtype=torch.bfloat16, device="cuda")
+        ops.attention_capped_prefill(paged.q[dev(keep, torch.int64)].contiguous(), paged.k_pages, paged.v_pages, part,
+                                     dev(new_start, torch.int32), dev(cut, torch.int32), paged.table, len(lengths),
+                                     max(lengths[i] - cut[i] for i in range(len(lengths))), nq, nkv, d, vd, scale,
+                                     window=window or None, value_heads=nv)
+        got_p = part.double().cpu().numpy().reshape(len(keep), nq, vd)
+        assert float(np.abs(got_p - got_t[keep]).max()) <= 2e-2
+        picks = [(0, p) for p in (0, 1, 63, 64, 65, 127, 128, 200, 299)] + [(1, 64), (2, 0), (3, 199), (3, 135), (3, 136), (3, 137)]
+        if window > 1:
+            picks += [(0, window - 1), (0, window), (0, window + 1)]
+        rows_at = np.array([start[s_] + p for s_, p in picks])
+        for splits in (1, 3, 16):
+            one = torch.full((len(picks), nq * vd), 5.0, dtype=torch.float32, device="cuda")
+            scratch = torch.full((len(picks) * nq * splits * (vd + 2),), float("nan"), dtype=torch.float32, device="cuda")
+            ops.attention_capped_decode(paged.q[dev(rows_at, torch.int64)].contiguous(), paged.k_pages, paged.v_pages, one, scratch,
+                                        dev([s_ for s_, _ in picks], torch.int32), dev([p for _, p in picks], torch.int32), paged.table,
+                                        len(picks), nq, nkv, d, vd, scale, 0.0, None, False, splits, window=window or None, value_heads=nv)
+            got_d = one.double().cpu().numpy().reshape(len(picks), nq, vd)
+            for i, (s_, p) in enumerate(picks):
+                for h in range(nq):
+                    assert float(np.abs(got_d[i, h] - wants[s_, h][p]).max()) <= 3e-2, ("decode", splits, s_, p, h)
     # the test has teeth: with the window off by one in either direction the plain result moves by far more than that
     if window > 1:
         block = rd[:lengths[0]]
