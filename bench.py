@@ -3,6 +3,7 @@ model with random weights in bfloat16 on one B200, batch 8 at a context of 4,096
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 8b|14b|32b]
     python bench.py --designs        (another measurement: a Dozazen model beside Qwen3 at equal sizes)
+    python bench.py --designs lagulorn   (the same for a Lagulorn model)
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.
   value     decoded tokens a second, timed on the device with CUDA events around K steps;
@@ -408,6 +409,44 @@ def design_point(q, torch, Sampler, cfg, rng, batch, context, steps, warmup):
     return out
 
 
+def lagulorn_config(width, heads, kv, d, ff, layers, window=1024, experts=16, top=2):
+    """A Lagulorn model of the widths of the Qwen3 model beside it: differential attention (two maps of d / 2 per head, values
+    of d) and lightning layers (heads of d x d) in turn, the first layer's feed-forward dense, the others routed (`experts`
+    experts of ff / (2 top), `top` of them per token: a token passes through half as many feed-forward rows as in the dense
+    model, and all experts together hold four times its weights), two streams of hidden state, every other lightning layer with the weights of the first."""
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": d // 2, "vdim": d, "scale": (d // 2) ** -0.5,
+                                                 "diff": 0.3, "mask": {"size": window}}}
+    lightning = {"type": "lightning", "mixer": {"heads": heads, "dim": d, "vdim": d,
+                                                 "decay": [1.0 - 2.0 ** -(3 + 5 * h / max(heads - 1, 1)) for h in range(heads)]}}
+    moe = {"kind": "moe", "expert": {"ff": ff // (2 * top), "limit": 7.0},
+           "router": {"experts": experts, "top": top, "identity": 0, "groups": {"count": 4, "keep": 2}}}
+    rows, first_lightning = [], None
+    for i in range(layers):
+        layer = dict(attention if i % 2 == 0 else lightning, mlp={"kind": "dense", "ff": ff} if i == 0 else moe)
+        if i % 2 == 1 and first_lightning is not None:
+            layer["weights_of"] = first_lightning
+        elif i % 2 == 1:
+            first_lightning = i
+        rows.append(layer)
+    return {"architecture": "Lagulorn", "vocab": DESIGN_VOCAB, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "residual_mult": 1.0, "streams": 2, "layers": rows}
+
+
+def lagulorn_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096):
+    """Lagulorn beside Qwen3 at equal widths (random weights, bfloat16): decode at `batch` x `context`, a prompt step of 2,048
+    tokens, and the time of every kernel of one step of each kind."""
+    import numpy as np
+    out = {"batch": batch, "context": context, "prompt_tokens": PREFILL_TOKENS, "vocab": DESIGN_VOCAB, "sizes": {}}
+    for name, width, heads, kv, d, ff, layers in DESIGN_SIZES:
+        row = {"width": width, "heads": heads, "kv_heads": kv, "head_dim": d, "ff": ff, "layers": layers}
+        row["lagulorn"] = design_point(q, torch, Sampler, lagulorn_config(width, heads, kv, d, ff, layers), np.random.default_rng(0),
+                                       batch, context, steps, warmup)
+        row["qwen3"] = design_point(q, torch, Sampler, design_configs(width, heads, kv, d, ff, layers, 8192)[1],
+                                    np.random.default_rng(0), batch, context, steps, warmup)
+        out["sizes"][name] = row
+    return out
+
+
 def designs_side_by_side(q, torch, Sampler, steps, warmup, batch=8, context=4096):
     """Dozazen beside Qwen3 at equal sizes (random weights, bfloat16): decode at `batch` x `context`, a prompt step of
     2,048 tokens; chunks longer than the context (every key is read, as in Qwen3) and chunks of 1,024."""
@@ -443,9 +482,9 @@ def main() -> int:
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the benchmark: time every kernel of one decode step and of one 2,048-token prompt step "
                          "with CUDA events (steps launched afresh, not replayed) and print the sums per entry point")
-    ap.add_argument("--designs", action="store_true",
-                    help="instead of the benchmark: decode and prompt throughput of a Dozazen model beside the Qwen3 model of the "
-                         "same widths at two sizes, with the time of every kernel of one step of each kind")
+    ap.add_argument("--designs", nargs="?", const="dozazen", default=None, choices=["dozazen", "lagulorn"],
+                    help="instead of the benchmark: decode and prompt throughput of a Dozazen (default) or Lagulorn model beside "
+                         "the Qwen3 model of the same widths at two sizes, with the time of every kernel of one step of each kind")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -466,7 +505,8 @@ def main() -> int:
     cfg, CONTEXT, shape_batch = SHAPES[args.shape]
     if args.designs:
         torch.cuda.set_device(0)
-        print(json.dumps(designs_side_by_side(q, torch, Sampler, min(args.steps, 64), warmup, args.batch or 8, args.context or 4096)))
+        side_by_side = lagulorn_side_by_side if args.designs == "lagulorn" else designs_side_by_side
+        print(json.dumps(side_by_side(q, torch, Sampler, min(args.steps, 64), warmup, args.batch or 8, args.context or 4096)))
         return 0
     if args.products:
         torch.cuda.set_device(0)

@@ -16,16 +16,19 @@
 //   moe_combine : out[token] = T( sum_k weight_k y[slot(token, k)] + id_weight h[token] ).
 //
 // The products accumulate in 32-bit in ascending order of k whatever the tile a pair falls into, so a token's
-// result does not depend on what else is in the step.
+// result does not depend on what else is in the step.  Float tiles run on fmaf; bfloat16 tiles on the tensor cores
+// (mma.m16n8k16, see `mma` below) when the widths are multiples of 32, else on fmaf too.
 #include "common.cuh"
 
 namespace {
+
+__device__ __forceinline__ bool aligned16_device(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int MAX_TOP = 32;
 constexpr int MAX_OUTPUTS = 1024;
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const float* __restrict__ correction,
                  int* __restrict__ top_ids, float* __restrict__ top_w, float* __restrict__ id_weight, int hidden, int n_out,
                  int n_real, int top, int group_count, int group_keep) {
@@ -38,10 +41,21 @@ moe_route_kernel(const T* __restrict__ h, const T* __restrict__ w_router, const 
     const int64_t t = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const T* x = h + t * hidden;
-    for (int e = warp; e < n_out; e += 4) {
+    // a warp per router output; 16-byte packets when the rows allow it (the order of the sum is fixed either way)
+    constexpr int VEC = Pack<T>::N;
+    const bool packed = hidden % VEC == 0 && aligned16_device(x) && aligned16_device(w_router);
+    for (int e = warp; e < n_out; e += 8) {
         const T* w = w_router + (int64_t)e * hidden;
         float dot = 0.0f;
-        for (int c = lane; c < hidden; c += 32) dot = fmaf(to_f32<T>(w[c]), to_f32<T>(x[c]), dot);
+        if (packed) {
+            for (int c = lane * VEC; c < hidden; c += 32 * VEC) {
+                const Pack<T> wv = load_pack<T>(w + c), xv = load_pack<T>(x + c);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) dot = fmaf(wv.get(i), xv.get(i), dot);
+            }
+        } else {
+            for (int c = lane; c < hidden; c += 32) dot = fmaf(to_f32<T>(w[c]), to_f32<T>(x[c]), dot);
+        }
         dot = warp_sum(dot);
         if (lane == 0) z[e] = dot;
     }
@@ -277,6 +291,166 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
     }
 }
 
+// ---------------------------------------------------------------- the same two products on the tensor cores (bfloat16)
+// A block of 8 warps owns 64 pairs x 64 columns (of gate AND up in the first product): warp w works on rows
+// 16 (w % 4) .. + 15 and columns 32 (w / 4) .. + 31 with mma.m16n8k16 (bfloat16 in, 32-bit accumulators).  X rows
+// (gathered through the pairs' token numbers) and W rows arrive as 16-byte asynchronous copies into a ring of four
+// stages of 32 k-values, so a block keeps three stages in flight: with a handful of pairs per expert (a decode step)
+// the kernel streams each chosen expert's weights once.  Widths in steps of 32.
+namespace mma {
+constexpr int BM = 64, BN = 64, BK = 32, STAGES = 4;
+constexpr int ROW = (BK + 8) * 2;                       // bytes of a padded tile row: ldmatrix without bank conflicts
+constexpr int TILE = BM * ROW;                          // one 64 x 32 tile
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// acc0 (and acc1 with DUAL) [n-tile][4] of this warp: rows quad and quad + 8 of its 16, columns n * 8 + tq * 2, + 1 of its 32.
+template <bool DUAL>
+__device__ __forceinline__ void tile_product(const bf16* __restrict__ X, int64_t x_stride, const int* src_row, const bf16* __restrict__ W0,
+                                             const bf16* __restrict__ W1, int n_cols, int col0, int K, unsigned char* smem,
+                                             float (&acc0)[4][4], float (&acc1)[4][4]) {
+    constexpr int MATS = DUAL ? 3 : 2;                  // tiles per stage: X, W0 (, W1)
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quad = lane >> 2, tq = lane & 3;
+    const uint32_t base = smem_u32(smem);
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc0[n][e] = acc1[n][e] = 0.0f;
+    // this thread's copy per tile and stage: row tid / 4, 16-byte chunk tid % 4
+    const int lr = tid >> 2, lc = tid & 3;
+    const bf16* x_src = X + (int64_t)src_row[lr] * x_stride + lc * 8;
+    const int w_row = min(col0 + lr, n_cols - 1);       // a row beyond the matrix reads the last one; its results are dropped
+    const bf16* w0_src = W0 + (int64_t)w_row * K + lc * 8;
+    const bf16* w1_src = DUAL ? W1 + (int64_t)w_row * K + lc * 8 : nullptr;
+    const uint32_t dst = lr * ROW + lc * 16;
+    const int nk = K / BK;
+    auto issue = [&](int kb) {
+        if (kb < nk) {
+            const uint32_t stage = base + (kb % STAGES) * (MATS * TILE) + dst;
+            cp_async16(stage, x_src + kb * BK);
+            cp_async16(stage + TILE, w0_src + kb * BK);
+            if (DUAL) cp_async16(stage + 2 * TILE, w1_src + kb * BK);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    const int m0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;
+    const int krow = (lane & 7) + ((lane >> 4) << 3);
+    for (int kb = 0; kb < nk; ++kb) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                                // stage kb has landed for every thread; stage kb - 1 is free
+        issue(kb + STAGES - 1);
+        const unsigned char* xs = smem + (kb % STAGES) * (MATS * TILE);
+        const uint32_t ws0 = base + (kb % STAGES) * (MATS * TILE) + TILE, ws1 = ws0 + TILE;
+#pragma unroll
+        for (int kt = 0; kt < BK / 16; ++kt) {
+            uint32_t a[4];
+            const unsigned char* lo = xs + (m0 + quad) * ROW + (kt * 16 + tq * 2) * 2;
+            a[0] = *reinterpret_cast<const uint32_t*>(lo);
+            a[1] = *reinterpret_cast<const uint32_t*>(lo + 8 * ROW);
+            a[2] = *reinterpret_cast<const uint32_t*>(lo + 16);
+            a[3] = *reinterpret_cast<const uint32_t*>(lo + 8 * ROW + 16);
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp) {
+                uint32_t b[4];
+                const uint32_t off = (n0 + jp * 16 + krow) * ROW + (2 * kt + ((lane >> 3) & 1)) * 16;
+                ldmatrix_x4(b, ws0 + off);
+                mma_bf16(acc0[2 * jp], a, b[0], b[1]);
+                mma_bf16(acc0[2 * jp + 1], a, b[2], b[3]);
+                if (DUAL) {
+                    ldmatrix_x4(b, ws1 + off);
+                    mma_bf16(acc1[2 * jp], a, b[0], b[1]);
+                    mma_bf16(acc1[2 * jp + 1], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+__global__ void __launch_bounds__(256)
+moe_up_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gate_up, const int* __restrict__ offsets,
+              const int* __restrict__ pair_of_slot, bf16* __restrict__ act, int n_real, int top, int hidden, int ff, float limit,
+              float alpha) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int src_row[BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    int expert, row0, rows;
+    if (!find_tile<BM>(offsets, n_real, blockIdx.y, expert, row0, rows)) return;
+    if (threadIdx.x < BM) src_row[threadIdx.x] = pair_of_slot[row0 + min((int)threadIdx.x, rows - 1)] / top;
+    __syncthreads();
+    const int col0 = blockIdx.x * BN;
+    const bf16* wg = w_gate_up + (int64_t)expert * 2 * ff * hidden;
+    float g[4][4], u[4][4];
+    tile_product<true>(h, hidden, src_row, wg, wg + (int64_t)ff * hidden, ff, col0, hidden, smem, g, u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int rr = (warp & 3) * 16 + quad + (e >> 1) * 8, c = col0 + (warp >> 2) * 32 + n * 8 + tq * 2 + (e & 1);
+            if (rr < rows && c < ff) {
+                const float gv = fminf(g[n][e], limit), uv = fminf(fmaxf(u[n][e], -limit), limit);
+                act[(int64_t)(row0 + rr) * ff + c] = __float2bfloat16_rn(gv / (1.0f + expf(-alpha * gv)) * (uv + 1.0f));
+            }
+        }
+}
+
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const bf16* __restrict__ act, const bf16* __restrict__ w_down, const int* __restrict__ offsets, float* __restrict__ y,
+                int n_real, int hidden, int ff) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int src_row[BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    int expert, row0, rows;
+    if (!find_tile<BM>(offsets, n_real, blockIdx.y, expert, row0, rows)) return;
+    if (threadIdx.x < BM) src_row[threadIdx.x] = row0 + min((int)threadIdx.x, rows - 1);
+    __syncthreads();
+    const int col0 = blockIdx.x * BN;
+    float acc[4][4], unused[4][4];
+    tile_product<false>(act, ff, src_row, w_down + (int64_t)expert * hidden * ff, nullptr, hidden, col0, ff, smem, acc, unused);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int rr = (warp & 3) * 16 + quad + (e >> 1) * 8, c = col0 + (warp >> 2) * 32 + n * 8 + tq * 2 + (e & 1);
+            if (rr < rows && c < hidden) y[(int64_t)(row0 + rr) * hidden + c] = acc[n][e];
+        }
+}
+
+int experts_launch(const bf16* h, const bf16* w_gate_up, const bf16* w_down, const int* offsets, const int* pair_of_slot, bf16* act,
+                   float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha, cudaStream_t stream) {
+    const int tiles = (n_pairs + BM - 1) / BM + n_real;          // an upper bound on the row tiles of all experts together
+    if (tiles > 65535) return Q3_ERR_TOO_LARGE;
+    static Q3PerDevice up_ok, down_ok;
+    cudaError_t e = q3_allow_shared_memory(moe_up_kernel, STAGES * 3 * TILE, up_ok);
+    if (e == cudaSuccess) e = q3_allow_shared_memory(moe_down_kernel, STAGES * 2 * TILE, down_ok);
+    if (e != cudaSuccess) return (int)e;
+    int code = (int)q3_launch(moe_up_kernel, dim3((ff + BN - 1) / BN, tiles), dim3(256), STAGES * 3 * TILE, stream, h, w_gate_up,
+                              offsets, pair_of_slot, act, n_real, top, hidden, ff, limit, alpha);
+    if (code != 0) return code;
+    return (int)q3_launch(moe_down_kernel, dim3((hidden + BN - 1) / BN, tiles), dim3(256), STAGES * 2 * TILE, stream, act, w_down,
+                          offsets, y, n_real, hidden, ff);
+}
+}  // namespace mma
+
 template <typename T, int TM>
 int moe_experts_launch(const T* h, const T* w_gate_up, const T* w_down, const int* offsets, const int* pair_of_slot, T* act, float* y,
                        int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha, cudaStream_t stream) {
@@ -300,7 +474,7 @@ int moe_experts_launch(const T* h, const T* w_gate_up, const T* w_down, const in
             group_count <= 0 || n_out % group_count != 0 || group_keep <= 0 || group_keep > group_count ||                \
             n_tokens > 0x7fffffffLL)                                                                                      \
             return Q3_ERR_BAD_SIZE;                                                                                       \
-        return (int)q3_launch(moe_route_kernel<T>, dim3((unsigned)n_tokens), dim3(128), 0, (cudaStream_t)stream,          \
+        return (int)q3_launch(moe_route_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, (cudaStream_t)stream,          \
                               (const T*)h, (const T*)w_router, correction, top_ids, top_w, id_weight, hidden, n_out,      \
                               n_real, top, group_count, group_keep);                                                      \
     }                                                                                                                     \
@@ -330,6 +504,17 @@ Q3_EXPORT int q3_moe_sort(const int* top_ids, int n_pairs, int n_real, int* offs
     if (n_real < 0 || n_real > 4096) return Q3_ERR_BAD_SIZE;
     return (int)q3_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * n_real + 1) * sizeof(int), (cudaStream_t)stream, top_ids,
                           n_pairs, n_real, offsets, slot_of_pair, pair_of_slot);
+}
+
+// bfloat16 with both widths in steps of 32 (and 16-byte aligned rows): the tensor-core tiles; else the fmaf tiles.
+Q3_EXPORT int q3_moe_experts_tc_bf16(const void* h, const void* w_gate_up, const void* w_down, const int* offsets,
+                                     const int* pair_of_slot, void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff,
+                                     float limit, float alpha, void* stream) {
+    if (n_pairs <= 0 || n_real <= 0) return 0;
+    if (hidden % 32 != 0 || ff % 32 != 0 || hidden <= 0 || ff <= 0) return Q3_ERR_BAD_SIZE;
+    if (!aligned16(h) || !aligned16(w_gate_up) || !aligned16(w_down) || !aligned16(act)) return Q3_ERR_MISALIGNED;
+    return mma::experts_launch((const bf16*)h, (const bf16*)w_gate_up, (const bf16*)w_down, offsets, pair_of_slot, (bf16*)act, y, n_pairs,
+                               n_real, top, hidden, ff, limit, alpha, (cudaStream_t)stream);
 }
 
 Q3_MOE_EXPORTS(f32, float)

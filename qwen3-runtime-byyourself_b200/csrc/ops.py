@@ -564,6 +564,9 @@ def moe_sort(top_ids: torch.Tensor, n_pairs: int, n_real: int, offsets: torch.Te
               _dev(slot_of_pair, "slot_of_pair", torch.int32), _dev(pair_of_slot, "pair_of_slot", torch.int32), _stream()), "moe_sort")
 
 
+moe_tensor_cores = True      # tests switch it off to run the fmaf tiles in bfloat16
+
+
 def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
                 act: torch.Tensor, y: torch.Tensor, n_pairs: int, n_real: int, top: int, ff: int, limit: float, alpha: float) -> None:
     """The experts' two products for the sorted pairs: act[slot] = g sigmoid(alpha g) (u + 1) with g = min(W_gate x, limit),
@@ -573,7 +576,9 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     if w_gate_up.numel() != n_real * 2 * ff * hidden or w_down.numel() != n_real * hidden * ff or act.numel() < n_pairs * ff \
             or y.numel() < n_pairs * hidden or y.dtype != torch.float32 or act.dtype != h.dtype or w_gate_up.dtype != h.dtype:
         raise KernelError("moe_experts: shapes do not fit")
-    fn = _fn("moe.cu", f"q3_moe_experts_{_suffix(h)}", [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    tensor_cores = h.dtype == torch.bfloat16 and hidden % 32 == 0 and ff % 32 == 0 and moe_tensor_cores
+    name = "q3_moe_experts_tc_bf16" if tensor_cores else f"q3_moe_experts_{_suffix(h)}"
+    fn = _fn("moe.cu", name, [c_void_p] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(fn(_dev(h, "h"), _dev(w_gate_up, "w_gate_up"), _dev(w_down, "w_down"), _dev(offsets, "offsets", torch.int32),
               _dev(pair_of_slot, "pair_of_slot", torch.int32), _dev(act, "act"), _dev(y, "y"), int(n_pairs), int(n_real), int(top),
               hidden, int(ff), float(limit), float(alpha), _stream()), "moe_experts")

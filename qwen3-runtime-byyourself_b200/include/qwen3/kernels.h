@@ -244,6 +244,10 @@ int q3_moe_experts_f32(const void* h, const void* w_gate_up, const void* w_down,
 int q3_moe_experts_bf16(const void* h, const void* w_gate_up, const void* w_down, const int* offsets, const int* pair_of_slot,
                         void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha,
                         void* stream);
+/* the same on the tensor cores: bfloat16, hidden and ff multiples of 32 */
+int q3_moe_experts_tc_bf16(const void* h, const void* w_gate_up, const void* w_down, const int* offsets, const int* pair_of_slot,
+                           void* act, float* y, int n_pairs, int n_real, int top, int hidden, int ff, float limit, float alpha,
+                           void* stream);
 /* out[t] = sum_k top_w[t, k] y[slot_of_pair[t, k]] + id_weight[t] h[t] */
 int q3_moe_combine_f32(const float* y, const void* h, const int* slot_of_pair, const float* top_w, const float* id_weight,
                        void* out, int64_t n_tokens, int top, int hidden, void* stream);

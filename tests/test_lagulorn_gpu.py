@@ -329,8 +329,9 @@ def test_router_scores_groups_choice_and_weights(outputs, real, top, groups, kee
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,ff", [(72, 40), (96, 64)])
 @pytest.mark.parametrize("N", [1, 7, 33, 300])
-def test_routed_experts_against_the_plain_feed_forward(dtype, N):
+def test_routed_experts_against_the_plain_feed_forward(dtype, N, hidden, ff):
     """The whole part: few tokens (the small tiles of a decode step) and many (large tiles, experts with several tiles
     and experts with none), identity experts, groups; a width and an expert size that are no multiples of the tiles."""
     import torch
@@ -338,7 +339,6 @@ def test_routed_experts_against_the_plain_feed_forward(dtype, N):
     from qwen3_b200.engine.context import Scratch
     rng = np.random.default_rng(N)
     T = torch_dtype(dtype)
-    hidden, ff = 72, 40
     mlp = {"expert": {"ff": ff, "limit": 0.8}, "router": {"experts": 6, "identity": 2, "top": 3, "groups": {"count": 4, "keep": 3}}}
     part = RoutedExperts(hidden, ff, 6, 3, 0.8, identity=2, group_count=4, group_keep=3, prefix="mlp.")
     tensors = lively_weights(part.weight_specs(""), 5)
