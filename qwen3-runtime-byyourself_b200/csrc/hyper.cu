@@ -36,8 +36,9 @@ __global__ void embedding_streams_kernel(const int* __restrict__ ids, const T* _
     }
 }
 
-// One block per row of the result.  The sum u of a token is kept in shared memory between the two passes.
-template <typename T, typename TO>
+// One block per row of the result.  The sum u of a token is kept in shared memory between the two passes.  VEC = 4:
+// 16-byte accesses to the streams (a hidden size in steps of 4); VEC = 1: any size.
+template <typename T, typename TO, int VEC>
 __global__ void hyper_norm_kernel(float* __restrict__ streams, const T* __restrict__ branch, const float* __restrict__ mix,
                                   const float* __restrict__ out_coef, const float* __restrict__ in_coef,
                                   const float* __restrict__ norm_w, float eps, TO* __restrict__ out,
@@ -59,43 +60,77 @@ __global__ void hyper_norm_kernel(float* __restrict__ streams, const T* __restri
     float* xs = streams + t * S * hidden;
     const T* y = branch != nullptr ? branch + t * hidden : nullptr;
     float sq = 0.0f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float x[MAX_STREAMS];
+    for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
+        float x[MAX_STREAMS][VEC], yv[VEC], u[VEC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s) x[s] = s < S ? xs[(int64_t)s * hidden + c] : 0.0f;
-        float u = 0.0f;
+        for (int s = 0; s < MAX_STREAMS; ++s) {
+            if (s < S) {
+                if constexpr (VEC == 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(xs + (int64_t)s * hidden + c);
+                    x[s][0] = v.x; x[s][1] = v.y; x[s][2] = v.z; x[s][3] = v.w;
+                } else {
+                    x[s][0] = xs[(int64_t)s * hidden + c];
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) u[i] = 0.0f;
         if (y != nullptr) {
-            const float yv = to_f32<T>(y[c]);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) yv[i] = to_f32<T>(y[c + i]);
 #pragma unroll
             for (int to = 0; to < MAX_STREAMS; ++to) {
                 if (to < S) {
-                    float v = 0.0f;
+                    float v[VEC];
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) v[i] = 0.0f;
 #pragma unroll
                     for (int from = 0; from < MAX_STREAMS; ++from)
-                        if (from < S) v = fmaf(c_mix[from * S + to], x[from], v);
-                    v = fmaf(c_out[to], yv, v);
-                    if (write_streams) xs[(int64_t)to * hidden + c] = v;
-                    u = fmaf(c_in[to], v, u);
+                        if (from < S) {
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) v[i] = fmaf(c_mix[from * S + to], x[from][i], v[i]);
+                        }
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) {
+                        v[i] = fmaf(c_out[to], yv[i], v[i]);
+                        u[i] = fmaf(c_in[to], v[i], u[i]);
+                    }
+                    if (write_streams) {
+                        if constexpr (VEC == 4)
+                            *reinterpret_cast<float4*>(xs + (int64_t)to * hidden + c) = make_float4(v[0], v[1], v[2], v[3]);
+                        else
+                            xs[(int64_t)to * hidden + c] = v[0];
+                    }
                 }
             }
         } else {
 #pragma unroll
             for (int s = 0; s < MAX_STREAMS; ++s)
-                if (s < S) u = fmaf(c_in[s], x[s], u);
+                if (s < S) {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) u[i] = fmaf(c_in[s], x[s][i], u[i]);
+                }
         }
         if (out != nullptr) {
-            u_s[c] = u;
-            sq += u * u;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                u_s[c + i] = u[i];
+                sq += u[i] * u[i];
+            }
         }
     }
     if (out == nullptr) return;
     TO* o = out + r * hidden;
     if (!normalize) {
-        for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<TO>(u_s[c]);     // the thread's own writes
+        for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC)     // the thread's own writes
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) o[c + i] = from_f32<TO>(u_s[c + i]);
         return;
     }
     const float inv = rsqrtf(block_sum(sq, scratch) / (float)hidden + eps);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = from_f32<TO>(u_s[c] * inv * norm_w[c]);
+    for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[c + i] = from_f32<TO>(u_s[c + i] * inv * norm_w[c + i]);
 }
 
 template <typename T, typename TO>
@@ -108,13 +143,19 @@ int hyper_norm_launch(float* streams, const T* branch, const float* mix, const f
     if (out != nullptr && normalize && norm_w == nullptr) return Q3_ERR_BAD_SIZE;
     const size_t smem = out != nullptr ? (size_t)hidden * sizeof(float) : 0;
     if (smem > 200 * 1024) return Q3_ERR_BAD_SIZE;
-    static Q3PerDevice allowed;
+    static Q3PerDevice allowed[2];
+    const bool vec = hidden % 4 == 0 && aligned16(streams);
     if (smem > 48 * 1024) {
-        const cudaError_t e = q3_allow_shared_memory(hyper_norm_kernel<T, TO>, 200 * 1024, allowed);
+        const cudaError_t e = vec ? q3_allow_shared_memory(hyper_norm_kernel<T, TO, 4>, 200 * 1024, allowed[1])
+                                  : q3_allow_shared_memory(hyper_norm_kernel<T, TO, 1>, 200 * 1024, allowed[0]);
         if (e != cudaSuccess) return (int)e;
     }
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    return (int)q3_launch(hyper_norm_kernel<T, TO>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
+    const int per = vec ? hidden / 4 : hidden;
+    const int threads = per >= 2048 ? 512 : (per >= 512 ? 256 : 128);
+    if (vec)
+        return (int)q3_launch(hyper_norm_kernel<T, TO, 4>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
+                              out_coef, in_coef, norm_w, eps, out, rows, S, hidden, normalize);
+    return (int)q3_launch(hyper_norm_kernel<T, TO, 1>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
                           out_coef, in_coef, norm_w, eps, out, rows, S, hidden, normalize);
 }
 

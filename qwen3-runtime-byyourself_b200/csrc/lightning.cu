@@ -219,7 +219,10 @@ int lightning_chunks_launch(const T* proj, float* state, const float* decay, con
                             float* out, int n_seqs, int H, int d, int vd, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || d <= 0 || vd <= 0 || d > 256 || vd > 256 || n_seqs > 65535) return Q3_ERR_BAD_SIZE;
-    const int vt = min(vd, COL_TILE);
+    // narrower column tiles while the blocks are fewer than the multiprocessors: a prompt of one sequence has only
+    // heads x tiles blocks, and a block's work per chunk shrinks with its tile (the scores alone are computed by every tile)
+    int vt = min(vd, COL_TILE);
+    while (vt > 16 && (int64_t)H * n_seqs * ((vd + vt - 1) / vt) < q3_device_sm_count()) vt /= 2;
     const int R = min(d, MAX_THREADS / vt);
     const int rows = (d + R - 1) / R;
     const int threads = ((vt * R + 31) / 32) * 32;

@@ -24,7 +24,6 @@ namespace {
 
 __device__ __forceinline__ bool aligned16_device(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-constexpr int MAX_TOP = 32;
 constexpr int MAX_OUTPUTS = 1024;
 
 template <typename T>
@@ -470,7 +469,7 @@ int moe_experts_launch(const T* h, const T* w_gate_up, const T* w_down, const in
                                         float* top_w, float* id_weight, int64_t n_tokens, int hidden, int n_out, int n_real, \
                                         int top, int group_count, int group_keep, void* stream) {                         \
         if (n_tokens <= 0) return 0;                                                                                      \
-        if (n_out <= 0 || n_out > MAX_OUTPUTS || top <= 0 || top > MAX_TOP || top > n_out || n_real < 0 || n_real > n_out || \
+        if (n_out <= 0 || n_out > MAX_OUTPUTS || top <= 0 || top > n_out || n_real < 0 || n_real > n_out || \
             group_count <= 0 || n_out % group_count != 0 || group_keep <= 0 || group_keep > group_count ||                \
             n_tokens > 0x7fffffffLL)                                                                                      \
             return Q3_ERR_BAD_SIZE;                                                                                       \
