@@ -322,7 +322,7 @@ __device__ __forceinline__ void tile_product(const bf16* __restrict__ X, int64_t
                                              const bf16* __restrict__ W1, int n_cols, int col0, int K, unsigned char* smem,
                                              float (&acc0)[4][4], float (&acc1)[4][4]) {
     constexpr int MATS = DUAL ? 3 : 2;                  // tiles per stage: X, W0 (, W1)
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quad = lane >> 2, tq = lane & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t base = smem_u32(smem);
 #pragma unroll
     for (int n = 0; n < 4; ++n)
@@ -353,16 +353,12 @@ __device__ __forceinline__ void tile_product(const bf16* __restrict__ X, int64_t
         cp_async_wait<STAGES - 2>();
         __syncthreads();                                // stage kb has landed for every thread; stage kb - 1 is free
         issue(kb + STAGES - 1);
-        const unsigned char* xs = smem + (kb % STAGES) * (MATS * TILE);
-        const uint32_t ws0 = base + (kb % STAGES) * (MATS * TILE) + TILE, ws1 = ws0 + TILE;
+        const uint32_t xs = base + (kb % STAGES) * (MATS * TILE);
+        const uint32_t ws0 = xs + TILE, ws1 = ws0 + TILE;
 #pragma unroll
         for (int kt = 0; kt < BK / 16; ++kt) {
-            uint32_t a[4];
-            const unsigned char* lo = xs + (m0 + quad) * ROW + (kt * 16 + tq * 2) * 2;
-            a[0] = *reinterpret_cast<const uint32_t*>(lo);
-            a[1] = *reinterpret_cast<const uint32_t*>(lo + 8 * ROW);
-            a[2] = *reinterpret_cast<const uint32_t*>(lo + 16);
-            a[3] = *reinterpret_cast<const uint32_t*>(lo + 8 * ROW + 16);
+            uint32_t a[4];                              // rows 0-7 and 8-15 of the warp's 16, k 0-7 and 8-15 of the step
+            ldmatrix_x4(a, xs + (m0 + (lane & 15)) * ROW + (kt * 16 + (lane >> 4) * 8) * 2);
 #pragma unroll
             for (int jp = 0; jp < 2; ++jp) {
                 uint32_t b[4];

@@ -18,4 +18,9 @@ def all_variants():
         ("stream_f32.cu", ()),
         ("attention_capped.cu", ("Q3_HEAD_DIM=128", "Q3_VALUE_DIM=128")),
         ("attention_prefill_tc.cu", ("Q3_HEAD_DIM=128", "Q3_CAPPED=1")),
+        ("hyper.cu", ()),
+        ("lightning.cu", ()),
+        ("differential.cu", ()),
+        ("moe.cu", ()),
+        ("attention_capped.cu", ("Q3_HEAD_DIM=64", "Q3_VALUE_DIM=128")),
     ]
