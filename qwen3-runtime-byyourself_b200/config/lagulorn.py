@@ -34,7 +34,7 @@ from .dozazen import MAX_POSITIONS, _get, _opt
 from .plan import LayerSpec, ModelPlan, PartSpec
 from .registry import ConfigError, register_architecture
 
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 
 
 @dataclass(frozen=True)

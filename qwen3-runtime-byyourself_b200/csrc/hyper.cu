@@ -18,7 +18,7 @@
 
 namespace {
 
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 
 template <typename T>
 __global__ void embedding_streams_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
@@ -37,9 +37,10 @@ __global__ void embedding_streams_kernel(const int* __restrict__ ids, const T* _
 }
 
 // One block per row of the result.  The sum u of a token is kept in shared memory between the two passes.  VEC = 4:
-// 16-byte accesses to the streams (a hidden size in steps of 4); VEC = 1: any size.
-template <typename T, typename TO, int VEC>
-__global__ void hyper_norm_kernel(float* __restrict__ streams, const T* __restrict__ branch, const float* __restrict__ mix,
+// 16-byte accesses to the streams (a hidden size in steps of 4); VEC = 1: any size.  SMAX bounds the streams a thread
+// keeps in registers (4 with 16-byte accesses, MAX_STREAMS without).
+template <typename T, typename TO, int VEC, int SMAX>
+__global__ void __launch_bounds__(512) hyper_norm_kernel(float* __restrict__ streams, const T* __restrict__ branch, const float* __restrict__ mix,
                                   const float* __restrict__ out_coef, const float* __restrict__ in_coef,
                                   const float* __restrict__ norm_w, float eps, TO* __restrict__ out,
                                   const int* __restrict__ rows, int S, int hidden, int normalize) {
@@ -51,19 +52,19 @@ __global__ void hyper_norm_kernel(float* __restrict__ streams, const T* __restri
     const int64_t r = blockIdx.x;
     const int64_t t = rows != nullptr ? rows[r] : r;
     const bool write_streams = rows == nullptr && branch != nullptr;
-    if (threadIdx.x < S * S && branch != nullptr) c_mix[threadIdx.x] = mix[threadIdx.x];
-    if (threadIdx.x < S) {
-        c_out[threadIdx.x] = branch != nullptr ? out_coef[threadIdx.x] : 0.0f;
-        c_in[threadIdx.x] = in_coef != nullptr ? in_coef[threadIdx.x] : 1.0f;
+    for (int i = threadIdx.x; i < S * S && branch != nullptr; i += blockDim.x) c_mix[i] = mix[i];
+    for (int i = threadIdx.x; i < S; i += blockDim.x) {
+        c_out[i] = branch != nullptr ? out_coef[i] : 0.0f;
+        c_in[i] = in_coef != nullptr ? in_coef[i] : 1.0f;
     }
     __syncthreads();
     float* xs = streams + t * S * hidden;
     const T* y = branch != nullptr ? branch + t * hidden : nullptr;
     float sq = 0.0f;
     for (int c = threadIdx.x * VEC; c < hidden; c += blockDim.x * VEC) {
-        float x[MAX_STREAMS][VEC], yv[VEC], u[VEC];
+        float x[SMAX][VEC], yv[VEC], u[VEC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s) {
+        for (int s = 0; s < SMAX; ++s) {
             if (s < S) {
                 if constexpr (VEC == 4) {
                     const float4 v = *reinterpret_cast<const float4*>(xs + (int64_t)s * hidden + c);
@@ -79,13 +80,13 @@ __global__ void hyper_norm_kernel(float* __restrict__ streams, const T* __restri
 #pragma unroll
             for (int i = 0; i < VEC; ++i) yv[i] = to_f32<T>(y[c + i]);
 #pragma unroll
-            for (int to = 0; to < MAX_STREAMS; ++to) {
+            for (int to = 0; to < SMAX; ++to) {
                 if (to < S) {
                     float v[VEC];
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) v[i] = 0.0f;
 #pragma unroll
-                    for (int from = 0; from < MAX_STREAMS; ++from)
+                    for (int from = 0; from < SMAX; ++from)
                         if (from < S) {
 #pragma unroll
                             for (int i = 0; i < VEC; ++i) v[i] = fmaf(c_mix[from * S + to], x[from][i], v[i]);
@@ -105,7 +106,7 @@ __global__ void hyper_norm_kernel(float* __restrict__ streams, const T* __restri
             }
         } else {
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; ++s)
+            for (int s = 0; s < SMAX; ++s)
                 if (s < S) {
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) u[i] = fmaf(c_in[s], x[s][i], u[i]);
@@ -143,20 +144,25 @@ int hyper_norm_launch(float* streams, const T* branch, const float* mix, const f
     if (out != nullptr && normalize && norm_w == nullptr) return Q3_ERR_BAD_SIZE;
     const size_t smem = out != nullptr ? (size_t)hidden * sizeof(float) : 0;
     if (smem > 200 * 1024) return Q3_ERR_BAD_SIZE;
-    static Q3PerDevice allowed[2];
-    const bool vec = hidden % 4 == 0 && aligned16(streams);
+    static Q3PerDevice allowed[3];
+    const bool vec = hidden % 4 == 0 && aligned16(streams) && S <= 4;
+    const bool few = S <= 4;
     if (smem > 48 * 1024) {
-        const cudaError_t e = vec ? q3_allow_shared_memory(hyper_norm_kernel<T, TO, 4>, 200 * 1024, allowed[1])
-                                  : q3_allow_shared_memory(hyper_norm_kernel<T, TO, 1>, 200 * 1024, allowed[0]);
+        const cudaError_t e = vec   ? q3_allow_shared_memory(hyper_norm_kernel<T, TO, 4, 4>, 200 * 1024, allowed[2])
+                              : few ? q3_allow_shared_memory(hyper_norm_kernel<T, TO, 1, 4>, 200 * 1024, allowed[1])
+                                    : q3_allow_shared_memory(hyper_norm_kernel<T, TO, 1, MAX_STREAMS>, 200 * 1024, allowed[0]);
         if (e != cudaSuccess) return (int)e;
     }
     const int per = vec ? hidden / 4 : hidden;
     const int threads = per >= 2048 ? 512 : (per >= 512 ? 256 : 128);
     if (vec)
-        return (int)q3_launch(hyper_norm_kernel<T, TO, 4>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
+        return (int)q3_launch(hyper_norm_kernel<T, TO, 4, 4>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
                               out_coef, in_coef, norm_w, eps, out, rows, S, hidden, normalize);
-    return (int)q3_launch(hyper_norm_kernel<T, TO, 1>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
-                          out_coef, in_coef, norm_w, eps, out, rows, S, hidden, normalize);
+    if (few)
+        return (int)q3_launch(hyper_norm_kernel<T, TO, 1, 4>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch, mix,
+                              out_coef, in_coef, norm_w, eps, out, rows, S, hidden, normalize);
+    return (int)q3_launch(hyper_norm_kernel<T, TO, 1, MAX_STREAMS>, dim3((unsigned)n_rows), dim3(threads), smem, stream, streams, branch,
+                          mix, out_coef, in_coef, norm_w, eps, out, rows, S, hidden, normalize);
 }
 
 }  // namespace

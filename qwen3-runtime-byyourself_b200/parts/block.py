@@ -144,6 +144,14 @@ class HyperConnectionBlock(Part):
             specs.update(self.feed_forward.weight_specs(prefix))
         return specs
 
+    def ignorable(self, prefix: str):
+        """Names that a checkpoint may hold although this block does not read them: the norm and connection tensors of
+        a feed-forward the layer does not have."""
+        if self.feed_forward is not None or len(self.names) < 2:
+            return []
+        c = self.connection_names[1] if len(self.connection_names) > 1 else None
+        return [prefix + self.names[1]] + ([prefix + c + k for k in ("in", "out", "mix")] if c else [])
+
     def bind(self, weights: dict, prefix: str, dtype, device) -> None:
         import torch
         for part, name in zip(self.norms, self.names):

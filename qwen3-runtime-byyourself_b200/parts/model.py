@@ -55,7 +55,10 @@ class Model:
         return specs
 
     def ignorable_names(self) -> List[str]:
-        return list(getattr(self.head, "ignorable", lambda prefix: [])(self.plan.head_prefix))
+        names = list(getattr(self.head, "ignorable", lambda prefix: [])(self.plan.head_prefix))
+        for spec, block in zip(self.plan.layers, self.blocks):
+            names += list(getattr(block, "ignorable", lambda prefix: [])(spec.prefix))
+        return names
 
     def bind(self, weights, dtype: torch.dtype, device) -> None:
         """Take the tensors (by checkpoint name) for computing in `dtype` on `device`.  `weights` is a dict of

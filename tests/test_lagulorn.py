@@ -30,6 +30,10 @@ def test_configuration_round_trip_and_plan(name):
     assert {f"l{i}.norm1" for i in owners} <= names and "embed" in names and "final.norm" in names and "head" in names
     assert not any(n.startswith(f"l{i}.") for n in names for i in range(len(cfg["layers"])) if i not in owners)
     assert (f"l{owners[0]}.hc1.mix" in names) == ("streams" in cfg)
+    # a layer without feed-forward reads no second norm; a file that holds one all the same still loads
+    for i in owners:
+        assert (f"l{i}.norm2" in model.ignorable_names()) == (cfg["layers"][i].get("mlp") is None)
+        assert (f"l{i}.norm2" in names) == (cfg["layers"][i].get("mlp") is not None)
     needs = model.cache_needs()
     for run, layer in enumerate(cfg["layers"]):
         need, m = needs[plan.caches[run]], layer["mixer"]
