@@ -486,11 +486,22 @@ def lightning_attention(proj: torch.Tensor, state: torch.Tensor, decay: torch.Te
             or out.dtype != torch.float32 or decay.numel() != heads:
         raise KernelError("lightning_attention: shapes do not fit")
     name = "chunks" if chunked else "scan"
+    if chunked and proj.dtype == torch.bfloat16 and lightning_tensor_cores and lightning_chunks_tc_fit(d, vd):
+        name = "chunks_tc"                                   # the chunks' products on the tensor cores (TF32 hi + lo operands)
     fn = _fn("lightning.cu", f"q3_lightning_{name}_{_suffix(proj)}", [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_dev(proj, "proj"), _dev(state, "state", torch.float32), _dev(decay, "decay", torch.float32),
               _dev(seq_start, "seq_start", torch.int32), _dev(seq_slots, "seq_slots", torch.int32), _dev(out, "out"),
               int(n_seqs), heads, d, vd, _stream()), f"lightning_{name}")
     return out
+
+
+lightning_tensor_cores = True      # tests switch it off to run the fmaf form of the chunks in bfloat16
+
+
+def lightning_chunks_tc_fit(d: int, vd: int) -> bool:
+    """Whether the tensor-core form of the chunks takes these head sizes: steps of 8, buffers within an SM's shared memory."""
+    dp = (d + 15) // 16 * 16
+    return d % 8 == 0 and vd % 8 == 0 and (2 * 32 * (dp + 4) + 32 * (min(vd, 64) + 8) + 32 * 36 + dp * (min(vd, 64) + 8)) * 4 <= 200 * 1024
 
 
 def lightning_chunks_fit(d: int, vd: int) -> bool:

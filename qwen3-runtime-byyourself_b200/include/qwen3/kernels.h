@@ -215,6 +215,9 @@ int q3_lightning_chunks_f32(const void* proj, float* state, const float* decay, 
                             float* out, int n_seqs, int heads, int d, int vd, void* stream);
 int q3_lightning_chunks_bf16(const void* proj, float* state, const float* decay, const int* seq_start, const int* seq_slots,
                              float* out, int n_seqs, int heads, int d, int vd, void* stream);
+/* the chunks' products on the tensor cores (operands as TF32 hi + lo terms): head sizes in steps of 8 */
+int q3_lightning_chunks_tc_bf16(const void* proj, float* state, const float* decay, const int* seq_start, const int* seq_slots,
+                                float* out, int n_seqs, int heads, int d, int vd, void* stream);
 /* out = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate), row by row; gate rows are gate_stride apart */
 int q3_gated_norm_f32(const float* o, const void* gate, int64_t gate_stride, const float* w, float eps, void* out,
                       int64_t n_tokens, int size, void* stream);

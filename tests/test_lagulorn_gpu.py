@@ -108,7 +108,11 @@ def test_lightning_recurrence_token_by_token_and_in_chunks(dtype, heads, d, vd):
     slots = [4, 0, 5, 2, 7, 1]
     cols = 2 * heads * (d + vd)
     chunked_ok = ops.lightning_chunks_fit(d, vd)
-    for chunked in ([False, True] if chunked_ok else [False]):
+    forms = [(False, False)] + ([(True, False)] if chunked_ok else [])
+    if dtype == "bfloat16" and ops.lightning_chunks_tc_fit(d, vd):
+        forms.append((True, True))                                # the chunks' products on the tensor cores
+    for chunked, tensor_cores in forms:
+        ops.lightning_tensor_cores = tensor_cores
         state = torch.zeros((9, heads, d, vd), dtype=torch.float32, device="cuda")
         state[3] = 7.0                                            # a slot no sequence uses
         want_state = {s: np.zeros((heads, d, vd)) for s in slots}
@@ -131,11 +135,12 @@ def test_lightning_recurrence_token_by_token_and_in_chunks(dtype, heads, d, vd):
                     o, want_state[slot][h] = plain_lightning(q, k, v, decay[h], want_state[slot][h])
                     scale = max(1.0, float(np.abs(o).max()))
                     err = float(np.abs(got[start[i]:start[i + 1], h * vd:(h + 1) * vd] - o).max())
-                    assert err <= 3e-5 * scale, (chunked, slot, h, err, scale)
+                    assert err <= 3e-5 * scale, (chunked, tensor_cores, slot, h, err, scale)
         final = state.double().cpu().numpy()
         for slot in slots:
             assert np.allclose(final[slot], want_state[slot], rtol=3e-5, atol=3e-5 * max(1.0, np.abs(want_state[slot]).max()))
         assert float((state[3] - 7.0).abs().max()) == 0.0 and float(state[6].abs().max()) == 0.0 and float(state[8].abs().max()) == 0.0
+    ops.lightning_tensor_cores = True
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
